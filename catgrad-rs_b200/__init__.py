@@ -13,4 +13,5 @@ from .backend import (  # noqa: F401
     F32, U32, PREC_F32, PREC_BF16, BackendError, BackendPanic, TaggedTensor, TraitBackend,
     CudaBackend, load_library, library_path,
 )
-from . import graphs  # noqa: F401
+from . import graphs, synth  # noqa: F401
+from .decoder import Decoder, DecoderConfig  # noqa: F401

@@ -1,0 +1,485 @@
+// attention.cu — fused attention over the device KV cache.
+//
+// What the reference computes with materialised [1, nh, S, S] scores
+// (catgrad-llm/src/models/llama.rs:97-108: q k^T / sqrt(d) + causal mask -> softmax -> v,
+// after repeat_kv, catgrad-llm/src/helpers.rs:147-161) is done here without the S x S
+// matrix: an online-softmax pass over key tiles.  Query head h reads kv head h / rep, the
+// order repeat_kv produces.  Masked scores are dropped, which equals adding f32::MIN before
+// the softmax (exp underflows to 0).
+//
+//   prefill: 64-query x 64-key tiles, bf16 mma.sync with f32 accumulation, 4 warps
+//   decode : one query per row; keys are streamed once per kv head for all its query
+//            heads, split over the context; a second kernel merges the splits
+#include "kernels.h"
+
+#include <algorithm>
+
+namespace cg {
+
+namespace {
+
+__device__ __forceinline__ float tanh_sig(float x) { return 2.f / (1.f + __expf(-2.f * x)) - 1.f; }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&v;
+}
+
+// ------------------------------------------------------------------ prefill ----------
+template <int D>
+__global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
+  constexpr int BQ = 64, BKV = 64, LD = D + 8;  // padded rows: conflict-free ldmatrix
+  extern __shared__ __align__(16) uint8_t smem[];
+  __nv_bfloat16* sq = (__nv_bfloat16*)smem;
+  __nv_bfloat16* sk = sq + BQ * LD;
+  __nv_bfloat16* sv = sk + BKV * LD;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = blockIdx.x, h = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  const int kvh = h / (a.nh / a.nkv);
+  const int64_t q0 = (int64_t)qt * BQ;
+  const __nv_bfloat16* qbase = a.q + (b * a.S) * (int64_t)a.nh * D + (int64_t)h * D;
+  const __nv_bfloat16* kbase = a.k_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
+  const __nv_bfloat16* vbase = a.v_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
+
+  // Q tile -> shared (rows past S are zero)
+  constexpr int CH = D / 8;  // 16-byte chunks per row
+  for (int i = tid; i < BQ * CH; i += 128) {
+    const int r = i / CH, ch = i - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (q0 + r < a.S) v = *(const uint4*)(qbase + (q0 + r) * (int64_t)a.nh * D + ch * 8);
+    *(uint4*)(sq + r * LD + ch * 8) = v;
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+
+  const int r_in = lane >> 2, cq = (lane & 3) * 2;
+  const int64_t qpos[2] = {a.pos0 + q0 + warp * 16 + r_in, a.pos0 + q0 + warp * 16 + r_in + 8};
+  const int64_t kv_len = a.pos0 + a.S;
+  const int64_t last_q = a.pos0 + std::min<int64_t>(a.S, q0 + BQ) - 1;  // last query position of this tile
+  int64_t first_k = 0;
+  if (a.window > 0) first_k = std::max<int64_t>(0, a.pos0 + q0 - a.window + 1);
+  const int64_t kt0 = first_k / BKV, kt1 = last_q / BKV;  // inclusive key tile range
+
+  const uint32_t sq_u = (uint32_t)__cvta_generic_to_shared(sq);
+  const uint32_t sk_u = (uint32_t)__cvta_generic_to_shared(sk);
+  const uint32_t sv_u = (uint32_t)__cvta_generic_to_shared(sv);
+  const float LOG2E = 1.4426950408889634f;
+
+  for (int64_t kt = kt0; kt <= kt1; ++kt) {
+    const int64_t k0 = kt * BKV;
+    __syncthreads();  // previous tile fully consumed (and Q stored, first time)
+    for (int i = tid; i < BKV * CH; i += 128) {
+      const int r = i / CH, ch = i - r * CH;
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if (k0 + r < kv_len) {
+        kv = *(const uint4*)(kbase + (k0 + r) * (int64_t)D + ch * 8);
+        vv = *(const uint4*)(vbase + (k0 + r) * (int64_t)D + ch * 8);
+      }
+      *(uint4*)(sk + r * LD + ch * 8) = kv;
+      *(uint4*)(sv + r * LD + ch * 8) = vv;
+    }
+    __syncthreads();
+
+    // S = Q K^T for this warp's 16 rows x 64 keys
+    float s[BKV / 8][4];
+#pragma unroll
+    for (int j = 0; j < BKV / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a0, a1, a2, a3;
+      {
+        const int row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int col = kk * 16 + 8 * (lane >> 4);
+        ldsm_x4(sq_u + (row * LD + col) * 2, a0, a1, a2, a3);
+      }
+#pragma unroll
+      for (int j = 0; j < BKV / 8; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int key = j * 8 + (lane & 7) + 8 * (lane >> 4);
+        const int col = kk * 16 + 8 * ((lane >> 3) & 1);
+        ldsm_x4(sk_u + (key * LD + col) * 2, b0, b1, b2, b3);
+        mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+
+    // scale, soft-cap, mask; row maxima
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < BKV / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t kpos = k0 + j * 8 + cq + (e & 1);
+        const int64_t qp = qpos[e >> 1];
+        float v = s[j][e] * scale;
+        if (a.softcap > 0.f) v = a.softcap * tanh_sig(v / a.softcap);
+        const bool keep = kpos <= qp && kpos < kv_len && (a.window <= 0 || kpos > qp - a.window);
+        v = keep ? v : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mnew = fmaxf(mrow[r], mx[r]);
+      msafe[r] = mnew == -INFINITY ? 0.f : mnew;
+      corr[r] = exp2f((mrow[r] - msafe[r]) * LOG2E);  // 0 when mrow is -inf
+      mrow[r] = mnew;
+    }
+    float ls[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < BKV / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f((s[j][e] - msafe[e >> 1]) * LOG2E);
+        s[j][e] = p;
+        ls[e >> 1] += p;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 1);
+      ls[r] += __shfl_xor_sync(0xffffffffu, ls[r], 2);
+      lrow[r] = lrow[r] * corr[r] + ls[r];
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= corr[0];
+      o[j][1] *= corr[0];
+      o[j][2] *= corr[1];
+      o[j][3] *= corr[1];
+    }
+
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < BKV / 16; ++kk) {
+      const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      const uint32_t a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int j = 0; j < D / 8; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int col = j * 8 + 8 * (lane >> 4);
+        ldsm_x4_t(sv_u + (key * LD + col) * 2, b0, b1, b2, b3);
+        mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
+        mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+
+  // normalise and store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int64_t qi = q0 + warp * 16 + r_in + 8 * r;
+    if (qi >= a.S) continue;
+    const float inv = lrow[r] > 0.f ? 1.f / lrow[r] : 0.f;
+    __nv_bfloat16* dst = a.out + (b * a.S + qi) * (int64_t)a.nh * D + (int64_t)h * D;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+      *(__nv_bfloat162*)(dst + j * 8 + cq) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decode -----------
+constexpr int DEC_SPLITS = 8;   // context slices per (row, kv head)
+constexpr int MAX_REP = 8;      // query heads per kv head supported by the decode kernel
+
+// scratch layout per (b, h, split): [m, l, o[0..d)]
+template <int D>
+__global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, int rep) {
+  constexpr int E = D / 32;  // output elements per lane
+  __shared__ float qs[MAX_REP][D];
+  __shared__ float ps[4][MAX_REP][32];
+  __shared__ float red_m[4][MAX_REP], red_l[4][MAX_REP];
+  __shared__ float red_o[4][MAX_REP][D];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.x, split = blockIdx.z;
+  const int64_t b = blockIdx.y;
+  const int64_t qp = a.pos_dev ? *a.pos_dev : a.pos0;
+  const int64_t T = qp + 1;  // keys visible to the new token
+  int64_t lo = 0;
+  if (a.window > 0) lo = std::max<int64_t>(0, qp - a.window + 1);
+  const int64_t span = T - lo;
+  const int64_t per = (span + DEC_SPLITS - 1) / DEC_SPLITS;
+  const int64_t t0 = lo + split * per, t1 = std::min<int64_t>(T, t0 + per);
+
+  const __nv_bfloat16* qbase = a.q + b * (int64_t)a.nh * D + (int64_t)kvh * rep * D;
+  for (int i = tid; i < rep * D; i += 128) qs[i / D][i % D] = __bfloat162float(qbase[i]);
+  __syncthreads();
+
+  const __nv_bfloat16* kbase = a.k_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
+  const __nv_bfloat16* vbase = a.v_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
+
+  float m[MAX_REP], l[MAX_REP], o[MAX_REP][E];
+#pragma unroll
+  for (int r = 0; r < MAX_REP; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) o[r][e] = 0.f;
+  }
+
+  for (int64_t c0 = t0 + warp * 32; c0 < t1; c0 += 4 * 32) {
+    const int64_t j = c0 + lane;
+    const bool valid = j < t1;
+    float sc[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; ++r) sc[r] = 0.f;
+    if (valid) {
+      const uint4* krow = (const uint4*)(kbase + j * (int64_t)D);
+#pragma unroll 4
+      for (int ch = 0; ch < D / 8; ++ch) {
+        const uint4 kv = krow[ch];
+        const __nv_bfloat162* k2 = (const __nv_bfloat162*)&kv;
+        float kf[8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(k2[t]);
+          kf[2 * t] = f.x;
+          kf[2 * t + 1] = f.y;
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_REP; ++r) {
+          if (r < rep) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) sc[r] += qs[r][ch * 8 + t] * kf[t];
+          }
+        }
+      }
+    }
+    float corr[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; ++r) {
+      if (r < rep) {
+        float v = sc[r] * scale;
+        if (a.softcap > 0.f) v = a.softcap * tanh_sig(v / a.softcap);
+        v = valid ? v : -INFINITY;
+        float mx = v;
+#pragma unroll
+        for (int s = 16; s; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        const float mnew = fmaxf(m[r], mx);  // finite: lane 0 of every chunk is valid
+        const float p = __expf(v - mnew);
+        float sum = p;
+#pragma unroll
+        for (int s = 16; s; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+        corr[r] = __expf(m[r] - mnew);
+        l[r] = l[r] * corr[r] + sum;
+        m[r] = mnew;
+        ps[warp][r][lane] = p;
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < MAX_REP; ++r)
+      if (r < rep) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[r][e] *= corr[r];
+      }
+    const int nk = (int)std::min<int64_t>(32, t1 - c0);
+    for (int jj = 0; jj < nk; ++jj) {
+      const __nv_bfloat16* vrow = vbase + (c0 + jj) * (int64_t)D + lane * E;
+      float vf[E];
+      if (E == 2) {
+        const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)vrow);
+        vf[0] = f.x;
+        vf[1] = f.y;
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; e += 2) {
+          const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)(vrow + e));
+          vf[e] = f.x;
+          vf[e + 1] = f.y;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < MAX_REP; ++r)
+        if (r < rep) {
+          const float p = ps[warp][r][jj];
+#pragma unroll
+          for (int e = 0; e < E; ++e) o[r][e] += p * vf[e];
+        }
+    }
+    __syncwarp();
+  }
+
+  // merge the four warps
+  for (int r = 0; r < rep; ++r) {
+    if (lane == 0) { red_m[warp][r] = m[r]; red_l[warp][r] = l[r]; }
+#pragma unroll
+    for (int e = 0; e < E; ++e) red_o[warp][r][lane * E + e] = o[r][e];
+  }
+  __syncthreads();
+  for (int i = tid; i < rep * D; i += 128) {
+    const int r = i / D, e = i % D;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w][r]);
+    float ll = 0.f, oo = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float f = red_m[w][r] == -INFINITY ? 0.f : __expf(red_m[w][r] - mm);
+      ll += red_l[w][r] * f;
+      oo += red_o[w][r][e] * f;
+    }
+    const int h = kvh * rep + r;
+    float* dst = a.scratch + (((b * a.nh + h) * DEC_SPLITS) + split) * (int64_t)(D + 2);
+    if (e == 0) { dst[0] = mm; dst[1] = ll; }
+    dst[2 + e] = oo;
+  }
+}
+
+template <int D>
+__global__ void k_attn_combine(const float* scratch, __nv_bfloat16* out, int nh) {
+  const int h = blockIdx.x;
+  const int64_t b = blockIdx.y;
+  const float* src = scratch + ((b * nh + h) * DEC_SPLITS) * (int64_t)(D + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < DEC_SPLITS; ++s) mm = fmaxf(mm, src[s * (D + 2)]);
+  for (int e = threadIdx.x; e < D; e += blockDim.x) {
+    float ll = 0.f, oo = 0.f;
+    for (int s = 0; s < DEC_SPLITS; ++s) {
+      const float ms = src[s * (D + 2)];
+      const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
+      ll += src[s * (D + 2) + 1] * f;
+      oo += src[s * (D + 2) + 2 + e] * f;
+    }
+    out[(b * nh + h) * (int64_t)D + e] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+  }
+}
+
+template <int D>
+int launch_prefill(cg_ctx* c, const AttnArgs& a) {
+  constexpr size_t smem = (size_t)3 * 64 * (D + 8) * 2;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    CG_CUDA(c, cudaFuncSetAttribute(k_attn_prefill<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((unsigned)((a.S + 63) / 64), (unsigned)a.nh, (unsigned)a.B);
+  const float scale = 1.0f / sqrtf((float)D);
+  k_attn_prefill<D><<<grid, 128, smem, c->core->stream>>>(a, scale);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+template <int D>
+int launch_decode(cg_ctx* c, const AttnArgs& a) {
+  const int rep = a.nh / a.nkv;
+  dim3 grid((unsigned)a.nkv, (unsigned)a.B, DEC_SPLITS);
+  const float scale = 1.0f / sqrtf((float)D);
+  k_attn_decode<D><<<grid, 128, 0, c->core->stream>>>(a, scale, rep);
+  CG_LAUNCHED(c);
+  dim3 g2((unsigned)a.nh, (unsigned)a.B);
+  k_attn_combine<D><<<g2, D < 128 ? 64 : 128, 0, c->core->stream>>>(a.scratch, a.out, a.nh);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int check(cg_ctx* c, const AttnArgs& a) {
+  if (a.nkv <= 0 || a.nh % a.nkv) return fail(c, CG_ERR_SHAPE, "attention: heads must be a multiple of kv heads");
+  if (a.d != 64 && a.d != 128 && a.d != 256) return fail(c, CG_ERR_UNSUPPORTED, "attention: head_dim must be 64, 128 or 256");
+  if (a.pos0 + a.S > a.Tmax) return fail(c, CG_ERR_SHAPE, "attention: KV cache capacity exceeded");
+  if (a.B > 65535 || a.nh > 65535) return fail(c, CG_ERR_UNSUPPORTED, "attention: too many rows or heads");
+  return CG_OK;
+}
+
+}  // namespace
+
+int64_t attn_decode_scratch_floats(int64_t B, int nh, int d) { return B * nh * DEC_SPLITS * (int64_t)(d + 2); }
+
+int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a) {
+  CG_TRY(check(c, a));
+  if (a.B == 0 || a.S == 0) return CG_OK;
+  switch (a.d) {
+    case 64: return launch_prefill<64>(c, a);
+    case 128: return launch_prefill<128>(c, a);
+    default: return launch_prefill<256>(c, a);
+  }
+}
+
+int k_launch_attn_decode(cg_ctx* c, const AttnArgs& a) {
+  CG_TRY(check(c, a));
+  if (a.S != 1) return fail(c, CG_ERR_INVALID, "attention decode takes one token per row");
+  if (a.nh / a.nkv > MAX_REP) return fail(c, CG_ERR_UNSUPPORTED, "attention decode: more than 8 query heads per kv head");
+  if (!a.scratch) return fail(c, CG_ERR_INVALID, "attention decode needs scratch");
+  if (a.B == 0) return CG_OK;
+  switch (a.d) {
+    case 64: return launch_decode<64>(c, a);
+    case 128: return launch_decode<128>(c, a);
+    default: return launch_decode<256>(c, a);
+  }
+}
+
+}  // namespace cg
+
+using namespace cg;
+
+extern "C" int32_t cg_fused_attention(cg_ctx* c, const cg_tensor* q, const cg_tensor* k, const cg_tensor* v, int64_t window,
+                                      float softcap, cg_tensor** out) {
+  if (!c || !q || !k || !v || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (q->tag != CG_F32 || k->tag != CG_F32 || v->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "attention wants F32 tensors");
+  if (q->rank != 4 || k->rank != 4 || v->rank != 4) return fail(c, CG_ERR_SHAPE, "attention wants [b, heads, s, d]");
+  const int64_t B = q->dims[0], nh = q->dims[1], S = q->dims[2], d = q->dims[3], nkv = k->dims[1];
+  for (int i = 0; i < 4; ++i)
+    if (k->dims[i] != v->dims[i]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  if (k->dims[0] != B || k->dims[2] != S || k->dims[3] != d) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  // bf16 copies in the layouts the kernel reads: q [B*S, nh*d], k/v [B, nkv, S, d]
+  Hold qt, qb, kb, vb, ob, r;
+  {
+    cg_tensor* t = nullptr;
+    CG_TRY(cg_transpose(c, q, 1, 2, &t));  // [B, S, nh, d] view
+    qt.t = t;
+  }
+  CG_TRY(cg_to_bf16(c, qt.t, &qb.t));
+  CG_TRY(cg_to_bf16(c, k, &kb.t));
+  CG_TRY(cg_to_bf16(c, v, &vb.t));
+  int64_t od[4] = {B, S, nh, d};
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, od, 4, &ob.t));
+  AttnArgs a;
+  a.q = (const __nv_bfloat16*)qb.t->data();
+  a.k_cache = (const __nv_bfloat16*)kb.t->data();
+  a.v_cache = (const __nv_bfloat16*)vb.t->data();
+  a.out = (__nv_bfloat16*)ob.t->data();
+  a.B = B; a.S = S; a.pos0 = 0; a.Tmax = S; a.pos_dev = nullptr;
+  a.nh = (int)nh; a.nkv = (int)nkv; a.d = (int)d;
+  a.window = window; a.softcap = softcap; a.scratch = nullptr;
+  CG_TRY(k_launch_attn_prefill(c, a));
+  // back to [B, nh, S, d] f32
+  Hold ot;
+  {
+    cg_tensor* t = nullptr;
+    CG_TRY(cg_transpose(c, ob.t, 1, 2, &t));
+    ot.t = t;
+  }
+  CG_TRY(cg_to_f32(c, ot.t, &r.t));
+  *out = r.take();
+  return CG_OK;
+}

@@ -1,0 +1,583 @@
+// decoder.cu — the greedy generation loop of catgrad-llm/examples/llama/main.rs:118-169 run
+// natively on the device, for decoder-only models of the Llama family
+// (catgrad-llm/src/models/llama.rs, with the switches of qwen3.rs / gemma3.rs).
+//
+// Where the reference recomputes the whole sequence for every generated token and passes
+// pos = 0 (llama.rs:170-178), this runner keeps a device KV cache with the semantics of
+// catgrad-llm/src/legacy/models/utils.rs:210-228 (append along the position axis), computes
+// the LM head on the last position only, and feeds each step's argmax to the next step
+// without a host round trip.  Position and token count live in device memory so that every
+// decode step is the same kernel sequence: it is captured once into a CUDA graph and
+// replayed.
+//
+// Data layout in HBM (per rank; heads, FFN columns and vocabulary are sharded over tp_world):
+//   w_qkv   [ (nh + 2 nkv) d, H ] bf16   rows = q heads, then k heads, then v heads
+//   w_o     [ H, nh d ]           bf16
+//   w_gu    [ 2 F, H ]            bf16   rows = gate, then up
+//   w_down  [ H, F ]              bf16
+//   embed   [ V, H ]              bf16   (also the LM head when tied)
+//   k/v     [ L ][ B, nkv, Tmax, d ] bf16
+//   x       [ M, H ] f32 residual stream; bf16 only where a tensor-core GEMM reads it
+
+#include <cstring>
+#include <map>
+#include <string>
+
+#include "kernels.h"
+#include "nccl_dl.h"
+
+using namespace cg;
+
+namespace {
+
+struct Layer {
+  cg_tensor *w_qkv = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr;
+  cg_tensor *ln_in = nullptr, *ln_post_attn = nullptr, *ln_pre_ffn = nullptr, *ln_post_ffn = nullptr;
+  cg_tensor *q_norm = nullptr, *k_norm = nullptr;
+  cg_tensor *k_cache = nullptr, *v_cache = nullptr;
+};
+
+void drop(cg_tensor*& t) {
+  if (t) release(t);
+  t = nullptr;
+}
+
+}  // namespace
+
+struct cg_decoder {
+  cg_ctx* c = nullptr;
+  cg_decoder_config cfg{};
+  std::map<std::string, cg_tensor*> params;  // as handed over, until finalize
+  bool finalized = false;
+  // sharded sizes
+  int nh = 0, nkv = 0, d = 0, F = 0, Vp = 0, H = 0, qkv = 0;
+  std::vector<Layer> layers;
+  cg_tensor *embed = nullptr, *head = nullptr, *ln_f = nullptr;
+  cg_tensor *cos_t = nullptr, *sin_t = nullptr;
+  // state
+  cg_tensor* state = nullptr;     // int64[2] on device: {position, tokens generated}
+  cg_tensor* cur = nullptr;       // u32 [B]: the tokens the next step consumes
+  cg_tensor* history = nullptr;   // u32 [max_batch, max_seq]
+  cg_tensor* logits = nullptr;    // f32 [tp_world, B, Vp]
+  int64_t B = 0, pos = 0, generated = 0;
+  // workspace (sized for `cap` tokens)
+  int64_t cap = 0;
+  cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *hact = nullptr,
+            *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *attn_scratch = nullptr;
+  cudaGraphExec_t graph = nullptr;
+  int64_t graph_B = -1;
+  int64_t step_launches = 0;     // kernels in one decode step
+  int64_t splitk_floats = 0;
+
+  int64_t* pos_dev() { return (int64_t*)state->data(); }
+  int64_t* count_dev() { return (int64_t*)state->data() + 1; }
+};
+
+namespace {
+
+int get_param(cg_decoder* D, const std::string& name, cg_tensor** out, bool required = true) {
+  auto it = D->params.find(name);
+  if (it == D->params.end()) {
+    *out = nullptr;
+    return required ? fail(D->c, CG_ERR_INVALID, "decoder: missing parameter " + name) : CG_OK;
+  }
+  *out = it->second;
+  return CG_OK;
+}
+
+// bf16 copy of rows [r0, r0 + nr) x cols [c0, c0 + nc) of a 2-D parameter, into dst at row `at`
+int copy_block(cg_ctx* c, const cg_tensor* w, int64_t r0, int64_t nr, int64_t c0, int64_t nc, cg_tensor* dst, int64_t at) {
+  if (w->rank != 2 || r0 + nr > w->dims[0] || c0 + nc > w->dims[1] || nc != dst->dims[1] || at + nr > dst->dims[0])
+    return fail(c, CG_ERR_SHAPE, "decoder: parameter has an unexpected shape");
+  cg_tensor *a = nullptr, *b = nullptr, *cv = nullptr;
+  CG_TRY(cg_slice(c, w, 0, r0, nr, &a));
+  Hold ha(a);
+  CG_TRY(cg_slice(c, a, 1, c0, nc, &b));
+  Hold hb(b);
+  CG_TRY(cg_to_bf16(c, b, &cv));
+  Hold hc(cv);
+  CG_CUDA(c, cudaMemcpyAsync((char*)dst->data() + (size_t)at * nc * 2, cv->data(), (size_t)nr * nc * 2,
+                             cudaMemcpyDeviceToDevice, c->core->stream));
+  return CG_OK;
+}
+
+int norm_weight(cg_decoder* D, const std::string& name, int64_t n, cg_tensor** out, bool required = true) {
+  cg_tensor* p = nullptr;
+  CG_TRY(get_param(D, name, &p, required));
+  if (!p) { *out = nullptr; return CG_OK; }
+  if (p->numel() != n) return fail(D->c, CG_ERR_SHAPE, "decoder: " + name + " has an unexpected shape");
+  return as_contiguous_f32(D->c, p, out);
+}
+
+int ensure_workspace(cg_decoder* D, int64_t M) {
+  if (M <= D->cap) return CG_OK;
+  cg_ctx* c = D->c;
+  if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }  // it holds the old buffers
+  drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact); drop(D->tmp);
+  const int64_t H = D->H;
+  int64_t s2[2];
+  s2[0] = M; s2[1] = H;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->x));
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->xn));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->tmp));
+  s2[1] = D->qkv;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->qkvb));
+  s2[1] = (int64_t)D->nh * D->d;
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->q));
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->att));
+  s2[1] = 2 * (int64_t)D->F;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->gu));
+  s2[1] = D->F;
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->hact));
+  D->cap = M;
+  return CG_OK;
+}
+
+// y = x W^T (+ residual) with every rank's partial summed when the weight is row-split.
+// mode: 0 -> f32 out, 2 -> out = residual + product (residual may alias out).
+int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, void* out, const float* residual, int mode) {
+  const int64_t N = w->dims[0], K = w->dims[1];
+  const int splits = gemm_tc_pick_splits(M, N, K);
+  float* ws = (int64_t)splits * M * N <= D->splitk_floats ? (float*)D->splitk->data() : nullptr;
+  return gemm_tc(D->c, (const __nv_bfloat16*)xin->data(), K, (const __nv_bfloat16*)w->data(), K, out, N, residual, M, N, K,
+                 mode, splits, ws);
+}
+
+int all_reduce_f32(cg_decoder* D, float* p, int64_t n) {
+  cg_ctx* c = D->c;
+  if (D->cfg.tp_world <= 1) return CG_OK;
+  if (!c->comm) return fail(c, CG_ERR_COMM, "decoder: tensor parallelism needs cg_comm_init first");
+  ncclResult_t r = nccl().AllReduce(p, p, (size_t)n, ncclFloat32, ncclSum, (ncclComm_t)c->comm, c->core->stream);
+  if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllReduce: ") + nccl().GetErrorString(r));
+  return CG_OK;
+}
+
+// x += W-projection of `xin` (row-split under tensor parallelism), optionally through a
+// post-norm: x += rmsnorm(proj).
+int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm) {
+  cg_ctx* c = D->c;
+  const bool tp = D->cfg.tp_world > 1;
+  float* x = (float*)D->x->data();
+  if (!tp && !post_norm) return gemm(D, xin, M, w, x, x, 2);
+  float* t = (float*)D->tmp->data();
+  if (tp && !post_norm) {
+    // rank 0 folds the residual into its partial; the sum over ranks is the new x everywhere
+    CG_TRY(gemm(D, xin, M, w, t, x, D->cfg.tp_rank == 0 ? 2 : 0));
+    CG_TRY(all_reduce_f32(D, t, M * D->H));
+    CG_CUDA(c, cudaMemcpyAsync(x, t, (size_t)M * D->H * 4, cudaMemcpyDeviceToDevice, c->core->stream));
+    return CG_OK;
+  }
+  CG_TRY(gemm(D, xin, M, w, t, nullptr, 0));
+  CG_TRY(all_reduce_f32(D, t, M * D->H));
+  return k_launch_rmsnorm_add(c, t, (const float*)post_norm->data(), D->cfg.rms_eps, D->cfg.norm_plus_one, M, D->H, x);
+}
+
+// All layers for M = B * S new tokens at positions [pos0, pos0 + S); x holds the embeddings.
+int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_pos) {
+  cg_ctx* c = D->c;
+  const cg_decoder_config& cfg = D->cfg;
+  const int64_t M = B * S;
+  for (int li = 0; li < cfg.num_layers; ++li) {
+    Layer& L = D->layers[li];
+    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
+                            cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0));
+    RopeStoreArgs r;
+    r.qkv = (const float*)D->qkvb->data();
+    r.cos_t = (const float*)D->cos_t->data();
+    r.sin_t = (const float*)D->sin_t->data();
+    r.q_gamma = L.q_norm ? (const float*)L.q_norm->data() : nullptr;
+    r.k_gamma = L.k_norm ? (const float*)L.k_norm->data() : nullptr;
+    r.norm_eps = cfg.rms_eps;
+    r.norm_plus_one = cfg.norm_plus_one;
+    r.q_out = (__nv_bfloat16*)D->q->data();
+    r.k_cache = (__nv_bfloat16*)L.k_cache->data();
+    r.v_cache = (__nv_bfloat16*)L.v_cache->data();
+    r.M = M; r.S = S; r.pos0 = pos0; r.Tmax = cfg.max_seq;
+    r.pos_dev = from_dev_pos ? D->pos_dev() : nullptr;
+    r.nh = D->nh; r.nkv = D->nkv; r.d = D->d;
+    CG_TRY(k_launch_rope_store(c, r));
+    AttnArgs a;
+    a.q = (const __nv_bfloat16*)D->q->data();
+    a.k_cache = (const __nv_bfloat16*)L.k_cache->data();
+    a.v_cache = (const __nv_bfloat16*)L.v_cache->data();
+    a.out = (__nv_bfloat16*)D->att->data();
+    a.B = B; a.S = S; a.pos0 = pos0; a.Tmax = cfg.max_seq;
+    a.pos_dev = from_dev_pos ? D->pos_dev() : nullptr;
+    a.nh = D->nh; a.nkv = D->nkv; a.d = D->d;
+    const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
+    a.window = windowed ? cfg.sliding_window : 0;
+    a.softcap = cfg.attn_softcap;
+    a.scratch = (float*)D->attn_scratch->data();
+    if (S == 1) CG_TRY(k_launch_attn_decode(c, a));
+    else CG_TRY(k_launch_attn_prefill(c, a));
+    CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn));
+    const cg_tensor* ln2 = L.ln_pre_ffn;
+    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)ln2->data(), cfg.rms_eps, cfg.norm_plus_one,
+                            M, D->H, D->xn->data(), 1));
+    CG_TRY(gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0));
+    CG_TRY(k_launch_act_mul(c, (const float*)D->gu->data(), M, D->F, cfg.act, (__nv_bfloat16*)D->hact->data()));
+    CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn));
+  }
+  return CG_OK;
+}
+
+// Final norm on the last position of every row, LM head, greedy pick.
+int run_head(cg_decoder* D, int64_t B, int64_t S, bool advance) {
+  cg_ctx* c = D->c;
+  const cg_decoder_config& cfg = D->cfg;
+  CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data() + (S - 1) * D->H, S * D->H, (const float*)D->ln_f->data(),
+                          cfg.rms_eps, cfg.norm_plus_one, B, D->H, D->xl->data(), 1));
+  float* lg = (float*)D->logits->data();
+  float* mine = lg + (int64_t)cfg.tp_rank * B * D->Vp;
+  CG_TRY(gemm(D, D->xl, B, D->head, mine, nullptr, 0));
+  if (cfg.tp_world > 1) {
+    if (!c->comm) return fail(c, CG_ERR_COMM, "decoder: tensor parallelism needs cg_comm_init first");
+    ncclResult_t r = nccl().AllGather(mine, lg, (size_t)(B * D->Vp), ncclFloat32, (ncclComm_t)c->comm, c->core->stream);
+    if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllGather: ") + nccl().GetErrorString(r));
+  }
+  return k_launch_argmax(c, lg, B, D->Vp, cfg.tp_world, cfg.final_softcap, (uint32_t*)D->cur->data(),
+                         (uint32_t*)D->history->data(), cfg.max_seq, D->count_dev(), D->pos_dev(), advance ? 1 : 0);
+}
+
+// One decode step for B rows reading position / count from device memory.
+int enqueue_step(cg_decoder* D, int64_t B) {
+  cg_ctx* c = D->c;
+  CG_TRY(k_launch_embed(c, (const uint32_t*)D->cur->data(), 1, 0, 1, D->embed->data(), D->embed->storage, D->cfg.vocab, B,
+                        D->H, D->cfg.embed_scale > 0.f ? D->cfg.embed_scale : 1.f, (float*)D->x->data()));
+  CG_TRY(run_layers(D, B, 1, 0, true));
+  return run_head(D, B, 1, true);
+}
+
+int logits_copy(cg_decoder* D, cg_tensor** out) {
+  if (!out) return CG_OK;
+  cg_ctx* c = D->c;
+  const int W = D->cfg.tp_world;
+  int64_t od[2] = {D->B, (int64_t)D->Vp * W};
+  Hold r;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, od, 2, &r.t));
+  // [W, B, Vp] -> [B, W * Vp]
+  for (int w = 0; w < W; ++w)
+    CG_CUDA(c, cudaMemcpy2DAsync((float*)r.t->data() + (int64_t)w * D->Vp, (size_t)od[1] * 4,
+                                 (const float*)D->logits->data() + (int64_t)w * D->B * D->Vp, (size_t)D->Vp * 4,
+                                 (size_t)D->Vp * 4, (size_t)D->B, cudaMemcpyDeviceToDevice, c->core->stream));
+  *out = r.take();
+  return CG_OK;
+}
+
+int set_state(cg_decoder* D, int64_t pos, int64_t generated) {
+  int64_t v[2] = {pos, generated};
+  CG_CUDA(D->c, cudaMemcpyAsync(D->state->data(), v, 16, cudaMemcpyHostToDevice, D->c->core->stream));
+  CG_CUDA(D->c, cudaStreamSynchronize(D->c->core->stream));  // `v` is on the stack
+  D->pos = pos;
+  D->generated = generated;
+  return CG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** out) {
+  if (!c || !cfg || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  const cg_decoder_config& k = *cfg;
+  if (k.num_layers <= 0 || k.hidden <= 0 || k.n_heads <= 0 || k.n_kv_heads <= 0 || k.head_dim <= 0 || k.ffn <= 0 ||
+      k.vocab <= 0 || k.max_seq <= 0 || k.max_batch <= 0)
+    return fail(c, CG_ERR_INVALID, "decoder: sizes must be positive");
+  if (k.n_experts > 0) return fail(c, CG_ERR_UNSUPPORTED, "decoder: mixture-of-experts layers are not built yet");
+  const int W = k.tp_world < 1 ? 1 : k.tp_world;
+  if (k.tp_rank < 0 || k.tp_rank >= W) return fail(c, CG_ERR_INVALID, "decoder: tp_rank out of range");
+  if (k.n_heads % k.n_kv_heads || k.n_heads % W || k.n_kv_heads % W || k.ffn % W || k.vocab % W)
+    return fail(c, CG_ERR_SHAPE, "decoder: heads, kv heads, ffn and vocab must divide by the tensor-parallel degree");
+  if (k.hidden % 8 || (k.ffn / W) % 8 || (k.vocab / W) % 8 || k.head_dim % 8)
+    return fail(c, CG_ERR_UNSUPPORTED, "decoder: hidden, ffn, vocab shards and head_dim must be multiples of 8");
+  if (c->precision != CG_PREC_BF16) return fail(c, CG_ERR_UNSUPPORTED, "decoder: needs a bf16-precision context");
+  auto* D = new cg_decoder();
+  D->c = c;
+  D->cfg = k;
+  D->cfg.tp_world = W;
+  D->H = k.hidden;
+  D->nh = k.n_heads / W;
+  D->nkv = k.n_kv_heads / W;
+  D->d = k.head_dim;
+  D->F = k.ffn / W;
+  D->Vp = k.vocab / W;
+  D->qkv = (D->nh + 2 * D->nkv) * D->d;
+  *out = D;
+  return CG_OK;
+}
+
+int32_t cg_decoder_destroy(cg_decoder* D) {
+  if (!D) return CG_ERR_INVALID;
+  cudaStreamSynchronize(D->c->core->stream);
+  if (D->graph) cudaGraphExecDestroy(D->graph);
+  for (auto& kv : D->params) release(kv.second);
+  for (auto& L : D->layers) {
+    drop(L.w_qkv); drop(L.w_o); drop(L.w_gu); drop(L.w_down); drop(L.ln_in); drop(L.ln_post_attn);
+    if (L.ln_pre_ffn) drop(L.ln_pre_ffn);
+    drop(L.ln_post_ffn); drop(L.q_norm); drop(L.k_norm); drop(L.k_cache); drop(L.v_cache);
+  }
+  if (D->head != D->embed) drop(D->head);
+  drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
+  drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
+  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->attn_scratch);
+  delete D;
+  return CG_OK;
+}
+
+int32_t cg_decoder_set_param(cg_decoder* D, const char* name, const cg_tensor* t) {
+  if (!D || !name || !t) return CG_ERR_INVALID;
+  if (D->finalized) return fail(D->c, CG_ERR_INVALID, "decoder: already finalized");
+  const_cast<cg_tensor*>(t)->rc++;
+  auto it = D->params.find(name);
+  if (it != D->params.end()) { release(it->second); it->second = const_cast<cg_tensor*>(t); }
+  else D->params.emplace(name, const_cast<cg_tensor*>(t));
+  return CG_OK;
+}
+
+int32_t cg_decoder_finalize(cg_decoder* D) {
+  if (!D) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (D->finalized) return CG_OK;
+  const cg_decoder_config& cfg = D->cfg;
+  const int W = cfg.tp_world, R = cfg.tp_rank;
+  const int64_t H = D->H, d = D->d;
+  const int64_t nh_all = cfg.n_heads, nkv_all = cfg.n_kv_heads;
+  D->layers.resize(cfg.num_layers);
+  for (int li = 0; li < cfg.num_layers; ++li) {
+    Layer& L = D->layers[li];
+    const std::string p = "model.layers." + std::to_string(li) + ".";
+    cg_tensor *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    CG_TRY(get_param(D, p + "self_attn.q_proj.weight", &wq));
+    CG_TRY(get_param(D, p + "self_attn.k_proj.weight", &wk));
+    CG_TRY(get_param(D, p + "self_attn.v_proj.weight", &wv));
+    CG_TRY(get_param(D, p + "self_attn.o_proj.weight", &wo));
+    CG_TRY(get_param(D, p + "mlp.gate_proj.weight", &wg));
+    CG_TRY(get_param(D, p + "mlp.up_proj.weight", &wu));
+    CG_TRY(get_param(D, p + "mlp.down_proj.weight", &wd));
+    if (wq->rank != 2 || wq->dims[0] != nh_all * d || wk->rank != 2 || wk->dims[0] != nkv_all * d || wv->rank != 2 ||
+        wv->dims[0] != nkv_all * d)
+      return fail(c, CG_ERR_SHAPE, "decoder: attention projections have unexpected shapes");
+    int64_t s2[2] = {D->qkv, H};
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_qkv));
+    CG_TRY(copy_block(c, wq, (int64_t)R * D->nh * d, D->nh * d, 0, H, L.w_qkv, 0));
+    CG_TRY(copy_block(c, wk, (int64_t)R * D->nkv * d, D->nkv * d, 0, H, L.w_qkv, D->nh * d));
+    CG_TRY(copy_block(c, wv, (int64_t)R * D->nkv * d, D->nkv * d, 0, H, L.w_qkv, (D->nh + D->nkv) * d));
+    s2[0] = H; s2[1] = D->nh * d;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_o));
+    CG_TRY(copy_block(c, wo, 0, H, (int64_t)R * D->nh * d, D->nh * d, L.w_o, 0));
+    s2[0] = 2 * (int64_t)D->F; s2[1] = H;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_gu));
+    CG_TRY(copy_block(c, wg, (int64_t)R * D->F, D->F, 0, H, L.w_gu, 0));
+    CG_TRY(copy_block(c, wu, (int64_t)R * D->F, D->F, 0, H, L.w_gu, D->F));
+    s2[0] = H; s2[1] = D->F;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_down));
+    CG_TRY(copy_block(c, wd, 0, H, (int64_t)R * D->F, D->F, L.w_down, 0));
+    CG_TRY(norm_weight(D, p + "input_layernorm.weight", H, &L.ln_in));
+    if (cfg.post_norms) {
+      // four norms per layer (catgrad-llm/src/models/gemma3.rs:192-238)
+      CG_TRY(norm_weight(D, p + "post_attention_layernorm.weight", H, &L.ln_post_attn));
+      CG_TRY(norm_weight(D, p + "pre_feedforward_layernorm.weight", H, &L.ln_pre_ffn));
+      CG_TRY(norm_weight(D, p + "post_feedforward_layernorm.weight", H, &L.ln_post_ffn));
+    } else {
+      CG_TRY(norm_weight(D, p + "post_attention_layernorm.weight", H, &L.ln_pre_ffn));
+    }
+    if (cfg.qk_norm) {
+      CG_TRY(norm_weight(D, p + "self_attn.q_norm.weight", d, &L.q_norm));
+      CG_TRY(norm_weight(D, p + "self_attn.k_norm.weight", d, &L.k_norm));
+    }
+    int64_t s4[4] = {cfg.max_batch, D->nkv, cfg.max_seq, d};
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s4, 4, &L.k_cache));
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s4, 4, &L.v_cache));
+    CG_CUDA(c, cudaMemsetAsync(L.k_cache->data(), 0, (size_t)L.k_cache->numel() * 2, c->core->stream));
+    CG_CUDA(c, cudaMemsetAsync(L.v_cache->data(), 0, (size_t)L.v_cache->numel() * 2, c->core->stream));
+    // the originals of this layer are no longer needed
+    for (const char* n : {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                          "self_attn.o_proj.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"}) {
+      auto it = D->params.find(p + n);
+      if (it != D->params.end()) { release(it->second); D->params.erase(it); }
+    }
+  }
+  {
+    cg_tensor* e = nullptr;
+    CG_TRY(get_param(D, "model.embed_tokens.weight", &e));
+    if (e->rank != 2 || e->dims[0] != cfg.vocab || e->dims[1] != H) return fail(c, CG_ERR_SHAPE, "decoder: embedding shape");
+    if (e->storage == ST_BF16 && e->contiguous()) { e->rc++; D->embed = e; }
+    else CG_TRY(cg_to_bf16(c, e, &D->embed));
+    cg_tensor* hsrc = D->embed;
+    Hold htmp;
+    if (!cfg.tie_embeddings) {
+      cg_tensor* h = nullptr;
+      CG_TRY(get_param(D, "lm_head.weight", &h));
+      if (h->rank != 2 || h->dims[0] != cfg.vocab || h->dims[1] != H) return fail(c, CG_ERR_SHAPE, "decoder: lm_head shape");
+      if (h->storage == ST_BF16 && h->contiguous()) { h->rc++; htmp.t = h; }
+      else CG_TRY(cg_to_bf16(c, h, &htmp.t));
+      hsrc = htmp.t;
+    }
+    // this rank's vocabulary slice is a row range of the table: a view, no copy
+    cg_tensor* hv = nullptr;
+    CG_TRY(cg_slice(c, hsrc, 0, (int64_t)R * D->Vp, D->Vp, &hv));
+    D->head = hv;
+    CG_TRY(norm_weight(D, "model.norm.weight", H, &D->ln_f));
+  }
+  for (auto& kv : D->params) release(kv.second);
+  D->params.clear();
+  (void)W;
+
+  int64_t td[2] = {cfg.max_seq, d / 2};
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->cos_t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->sin_t));
+  CG_TRY(k_launch_rope_tables(c, cfg.rope_theta, cfg.max_seq, d, (float*)D->cos_t->data(), (float*)D->sin_t->data()));
+
+  int64_t n = 4;
+  CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->state));  // 16 bytes: two int64
+  n = cfg.max_batch;
+  CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->cur));
+  int64_t hd[2] = {cfg.max_batch, cfg.max_seq};
+  CG_TRY(new_tensor(c, CG_U32, ST_U32, hd, 2, &D->history));
+  int64_t ld[3] = {cfg.tp_world, cfg.max_batch, D->Vp};
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, ld, 3, &D->logits));
+  int64_t xd[2] = {cfg.max_batch, H};
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &D->xl));
+  // split-K partials: at most 32 slices of a [tokens <= 64, widest GEMM output] problem
+  const int64_t widest = std::max<int64_t>(std::max<int64_t>(D->qkv, 2 * (int64_t)D->F), std::max<int64_t>(H, D->Vp));
+  n = std::max<int64_t>(32 * 64 * widest, (int64_t)300 * 128 * 256);
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->splitk));
+  D->splitk_floats = n;
+  n = attn_decode_scratch_floats(cfg.max_batch, D->nh, D->d);
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->attn_scratch));
+  CG_TRY(ensure_workspace(D, cfg.max_batch));
+  CG_TRY(set_state(D, 0, 0));
+  D->finalized = true;
+  return cg_sync(c);
+}
+
+int32_t cg_decoder_reset(cg_decoder* D) {
+  if (!D || !D->finalized) return CG_ERR_INVALID;
+  D->B = 0;
+  return set_state(D, 0, 0);
+}
+
+int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  if (!D || !tokens) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
+  if (tokens->tag != CG_U32 || tokens->rank != 2) return fail(c, CG_ERR_SHAPE, "decoder: tokens must be U32 [B, S]");
+  const int64_t B = tokens->dims[0], S = tokens->dims[1];
+  if (B < 1 || B > D->cfg.max_batch || S < 1 || S > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: batch or length out of range");
+  Hold tk;
+  CG_TRY(as_contiguous(c, tokens, &tk.t));
+  CG_TRY(set_state(D, 0, 0));
+  D->B = B;
+  // the prompt is processed in position chunks so the workspace stays bounded
+  const int64_t chunk_tokens = 8192;
+  int64_t Sc = std::max<int64_t>(1, chunk_tokens / B);
+  if (Sc > 64) Sc = Sc / 64 * 64;
+  Sc = std::min(Sc, S);
+  CG_TRY(ensure_workspace(D, B * Sc));
+  for (int64_t p0 = 0; p0 < S; p0 += Sc) {
+    const int64_t s = std::min(Sc, S - p0);
+    CG_TRY(k_launch_embed(c, (const uint32_t*)tk.t->data(), S, p0, s, D->embed->data(), D->embed->storage, D->cfg.vocab,
+                          B * s, D->H, D->cfg.embed_scale > 0.f ? D->cfg.embed_scale : 1.f, (float*)D->x->data()));
+    // a one-token chunk would take the decode attention path, which reads the device position
+    if (s == 1) CG_TRY(set_state(D, p0, 0));
+    CG_TRY(run_layers(D, B, s, p0, s == 1));
+    if (p0 + s == S) {
+      CG_TRY(set_state(D, S, 0));
+      CG_TRY(run_head(D, B, s, false));
+      // count the prefill's token: generated = 1 (position stays S: that token is not cached yet)
+      int64_t v[2] = {S, 1};
+      CG_CUDA(c, cudaMemcpyAsync(D->state->data(), v, 16, cudaMemcpyHostToDevice, c->core->stream));
+      CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
+      D->pos = S;
+      D->generated = 1;
+    }
+  }
+  return logits_copy(D, logits_out);
+}
+
+int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) {
+  if (!D || steps < 0) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized || D->B == 0) return fail(c, CG_ERR_INVALID, "decoder: prefill first");
+  if (D->pos + steps > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: KV cache capacity exceeded");
+  if (steps == 0) return logits_copy(D, logits_out);
+  cudaStream_t s = c->core->stream;
+  if (!D->graph || D->graph_B != D->B) {
+    if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }
+    // Run one step eagerly first: it configures kernel attributes and surfaces errors
+    // outside of capture.  Then capture the identical sequence.
+    const int64_t before = c->launches;
+    CG_TRY(enqueue_step(D, D->B));
+    D->step_launches = c->launches - before;
+    D->pos += 1;
+    D->generated += 1;
+    steps -= 1;
+    cudaGraph_t g = nullptr;
+    CG_CUDA(c, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int st = enqueue_step(D, D->B);
+    cudaError_t e = cudaStreamEndCapture(s, &g);
+    c->launches = before + D->step_launches;  // capturing launched nothing
+    if (st != CG_OK) { if (g) cudaGraphDestroy(g); return st; }
+    if (e != cudaSuccess) return cuda_fail(c, e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(&D->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return cuda_fail(c, e, "cudaGraphInstantiate");
+    D->graph_B = D->B;
+  }
+  for (int i = 0; i < steps; ++i) CG_CUDA(c, cudaGraphLaunch(D->graph, s));
+  c->launches += (int64_t)steps * D->step_launches;  // each replay runs the captured kernels
+  D->pos += steps;
+  D->generated += steps;
+  return logits_copy(D, logits_out);
+}
+
+int32_t cg_decoder_step_with(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  if (!D || !tokens) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized || D->B == 0) return fail(c, CG_ERR_INVALID, "decoder: prefill first");
+  if (tokens->tag != CG_U32 || tokens->numel() != D->B) return fail(c, CG_ERR_SHAPE, "decoder: tokens must be U32 [B]");
+  if (D->pos + 1 > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: KV cache capacity exceeded");
+  Hold tk;
+  CG_TRY(as_contiguous(c, tokens, &tk.t));
+  CG_CUDA(c, cudaMemcpyAsync(D->cur->data(), tk.t->data(), (size_t)D->B * 4, cudaMemcpyDeviceToDevice, c->core->stream));
+  CG_TRY(enqueue_step(D, D->B));
+  D->pos += 1;
+  D->generated += 1;
+  return logits_copy(D, logits_out);
+}
+
+int32_t cg_decoder_tokens(cg_decoder* D, cg_tensor** out) {
+  if (!D || !out) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
+  cg_tensor *a = nullptr, *b = nullptr;
+  CG_TRY(cg_slice(c, D->history, 0, 0, D->B, &a));
+  Hold ha(a);
+  CG_TRY(cg_slice(c, a, 1, 0, D->generated, &b));
+  Hold hb(b);
+  return as_contiguous(c, b, out);
+}
+
+int32_t cg_decoder_generate(cg_decoder* D, const uint32_t* prompt, int32_t batch, int32_t seq, int32_t n_decode,
+                            uint32_t* out) {
+  if (!D || !prompt || !out || batch < 1 || seq < 1 || n_decode < 0) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  cg_tensor* tk = nullptr;
+  int64_t dims[2] = {batch, seq};
+  CG_TRY(cg_ndarray_from_vec_u32(c, prompt, (int64_t)batch * seq, dims, 2, &tk));
+  Hold htk(tk);
+  CG_TRY(cg_decoder_prefill(D, tk, nullptr));
+  const int64_t ld = 1 + (int64_t)n_decode;
+  std::vector<uint32_t> step((size_t)batch);
+  for (int i = 0; i <= n_decode; ++i) {
+    if (i > 0) CG_TRY(cg_decoder_decode(D, 1, nullptr));
+    // like the reference's per-step to_vec: read this step's tokens back before going on
+    CG_CUDA(c, cudaMemcpyAsync(step.data(), D->cur->data(), (size_t)batch * 4, cudaMemcpyDeviceToHost, c->core->stream));
+    CG_TRY(cg_sync(c));
+    for (int b = 0; b < batch; ++b) out[b * ld + i] = step[b];
+  }
+  return CG_OK;
+}
+
+}  // extern "C"

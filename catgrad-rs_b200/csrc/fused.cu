@@ -1,0 +1,472 @@
+// fused.cu — memory-bound fused kernels: each does in one pass over HBM what the reference
+// spreads over a chain of primitive backend calls with materialised intermediates
+// (catgrad/src/stdlib/nn/mod.rs:117-171, catgrad-llm/src/helpers.rs:120-271).
+// Rows are reduced with warp shuffles; loads are 128-bit where the row length allows.
+#include "kernels.h"
+
+#include <algorithm>
+
+namespace cg {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// block-wide sum / max (blockDim multiple of 32, <= 1024); sh holds 32 floats
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[wid] = v;
+  __syncthreads();
+  v = lane < nw ? sh[lane] : 0.f;
+  return warp_sum(v);
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) sh[wid] = v;
+  __syncthreads();
+  v = lane < nw ? sh[lane] : -INFINITY;
+  return warp_max(v);
+}
+
+// sigmoid / tanh / silu / gelu spelled as the stdlib composes them (nn/mod.rs:130-160)
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float tanh_f(float x) { return 2.f * sigmoid_f(2.f * x) - 1.f; }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
+__device__ __forceinline__ float gelu_f(float x) {
+  const float c = 0.7978845608f;  // sqrt(2/pi) in f32
+  return 0.5f * x * (1.f + tanh_f(c * (x + 0.044715f * x * x * x)));
+}
+
+__global__ void k_embed(const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,
+                        int64_t vocab, int64_t H, float scale, float* out, int32_t* err) {
+  const int64_t m = blockIdx.x;
+  const int64_t b = m / S, sp = m - b * S;
+  uint32_t t = tokens[b * tok_ld + tok_off + sp];
+  if (t >= vocab) { if (threadIdx.x == 0) *err = DEV_INDEX; t = 0; }
+  if (st == ST_BF16) {
+    const __nv_bfloat162* row = (const __nv_bfloat162*)((const __nv_bfloat16*)table + (int64_t)t * H);
+    float2* o = (float2*)(out + m * H);
+    for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) {
+      float2 v = __bfloat1622float2(row[i]);
+      o[i] = make_float2(v.x * scale, v.y * scale);
+    }
+    if ((H & 1) && threadIdx.x == 0)
+      out[m * H + H - 1] = __bfloat162float(((const __nv_bfloat16*)table)[(int64_t)t * H + H - 1]) * scale;
+  } else {
+    const float* row = (const float*)table + (int64_t)t * H;
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[m * H + i] = row[i] * scale;
+  }
+}
+
+// One block per row.  MODE 0: out f32, 1: out bf16, 2: x_acc += normed(y)
+template <int MODE>
+__global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t H, void* out) {
+  __shared__ float sh[32];
+  const int64_t m = blockIdx.x;
+  const float* row = x + m * ldx;
+  float ss = 0.f;
+  const bool vec = (H % 4 == 0) && (ldx % 4 == 0) && (((uintptr_t)x & 15) == 0);
+  if (vec) {
+    const float4* r4 = (const float4*)row;
+    for (int64_t i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      float4 v = r4[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) ss += row[i] * row[i];
+  }
+  ss = block_sum(ss, sh);
+  const float rms = sqrtf(ss / (float)H + eps);
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+    const float g = plus_one ? 1.f + gamma[i] : gamma[i];
+    const float v = row[i] / rms * g;
+    if (MODE == 0) ((float*)out)[m * H + i] = v;
+    else if (MODE == 1) ((__nv_bfloat16*)out)[m * H + i] = __float2bfloat16_rn(v);
+    else ((float*)out)[m * H + i] += v;
+  }
+}
+
+__global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* out) {
+  const int64_t m = blockIdx.y;
+  const float* g = gu + m * 2 * F;
+  const float* u = g + F;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < F; i += (int64_t)gridDim.x * blockDim.x) {
+    const float a = act == 0 ? silu_f(g[i]) : gelu_f(g[i]);
+    out[m * F + i] = __float2bfloat16_rn(a * u[i]);
+  }
+}
+__global__ void k_act_mul_f32(const float* g, const float* u, int64_t n, int act, float* out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float a = act == 0 ? silu_f(g[i]) : gelu_f(g[i]);
+    out[i] = a * u[i];
+  }
+}
+
+// one block per row: softmax(x) or softmax(cap * tanh(x / cap))
+__global__ void k_softmax(const float* x, int64_t n, float softcap, float* out) {
+  __shared__ float sh[32];
+  const float* row = x + (int64_t)blockIdx.x * n;
+  float* o = out + (int64_t)blockIdx.x * n;
+  float mx = -3.4028234663852886e38f;  // the reference folds max from f32::MIN
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = row[i];
+    if (softcap > 0.f) v = softcap * tanh_f(v / softcap);
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, sh);
+  float s = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = row[i];
+    if (softcap > 0.f) v = softcap * tanh_f(v / softcap);
+    const float e = __expf(v - mx);
+    o[i] = e;
+    s += e;
+  }
+  s = block_sum(s, sh);
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) o[i] = o[i] / s;
+}
+
+// cos/sin tables as rope_tables builds them (helpers.rs:164-193): f = i * (2/d) rounded
+// twice, inv = 1 / theta^f, angle = pos * inv, all in f32; the transcendental functions go
+// through double like the elementwise pow/sin/cos kernels do.
+__global__ void k_rope_tables(float theta, int64_t T, int64_t half, float two_over_d, float* cos_t, float* sin_t) {
+  const int64_t n = T * half;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t pos = i / half, j = i - pos * half;
+    const float f = (float)j * two_over_d;
+    const float freq = (float)pow((double)theta, (double)f);
+    const float inv = 1.0f / freq;
+    const float ang = (float)pos * inv;
+    cos_t[i] = (float)cos((double)ang);
+    sin_t[i] = (float)sin((double)ang);
+  }
+}
+
+// x [rows, S, d] -> cos * x + sin * rotate_half(x), position pos0 + s
+__global__ void k_rope_apply(const float* x, const float* cos_t, const float* sin_t, int64_t S, int64_t d, int64_t pos0,
+                             int64_t n, float* out) {
+  const int64_t half = d / 2;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = i % d, s = (i / d) % S;
+    const int64_t j = e < half ? e : e - half;
+    const float c = cos_t[(pos0 + s) * half + j], sn = sin_t[(pos0 + s) * half + j];
+    const float rot = e < half ? -x[i + half] : x[i - half];
+    out[i] = c * x[i] + sn * rot;
+  }
+}
+
+// One warp per (token, head) of the fused qkv row: optional per-head RMSNorm, rotation,
+// bf16 store of q, append of k and v to the cache.
+__global__ void k_rope_store(RopeStoreArgs a) {
+  const int heads = a.nh + 2 * a.nkv;
+  const int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= a.M * heads) return;
+  const int64_t m = w / heads;
+  const int h = (int)(w - m * heads);
+  const int64_t b = m / a.S, s = m - b * a.S, pos = (a.pos_dev ? *a.pos_dev : a.pos0) + s;
+  const int d = a.d, half = d / 2;
+  const float* src = a.qkv + m * (int64_t)heads * d + (int64_t)h * d;
+  const bool is_q = h < a.nh, is_k = !is_q && h < a.nh + a.nkv;
+  __nv_bfloat16* dst;
+  if (is_q) dst = a.q_out + m * (int64_t)a.nh * d + (int64_t)h * d;
+  else if (is_k) dst = a.k_cache + (((int64_t)b * a.nkv + (h - a.nh)) * a.Tmax + pos) * d;
+  else dst = a.v_cache + (((int64_t)b * a.nkv + (h - a.nh - a.nkv)) * a.Tmax + pos) * d;
+  if (!is_q && !is_k) {
+    for (int e = lane; e < d; e += 32) dst[e] = __float2bfloat16_rn(src[e]);
+    return;
+  }
+  const float* gamma = is_q ? a.q_gamma : a.k_gamma;
+  float inv_rms = 1.f;
+  if (gamma) {
+    float ss = 0.f;
+    for (int e = lane; e < d; e += 32) ss += src[e] * src[e];
+    ss = warp_sum(ss);
+    inv_rms = 1.f / sqrtf(ss / (float)d + a.norm_eps);
+  }
+  for (int j = lane; j < half; j += 32) {
+    float x1 = src[j], x2 = src[j + half];
+    if (gamma) {
+      const float g1 = a.norm_plus_one ? 1.f + gamma[j] : gamma[j];
+      const float g2 = a.norm_plus_one ? 1.f + gamma[j + half] : gamma[j + half];
+      x1 = x1 * inv_rms * g1;
+      x2 = x2 * inv_rms * g2;
+    }
+    const float c = a.cos_t[pos * half + j], sn = a.sin_t[pos * half + j];
+    dst[j] = __float2bfloat16_rn(c * x1 - sn * x2);
+    dst[j + half] = __float2bfloat16_rn(c * x2 + sn * x1);
+  }
+}
+
+// argmax over the vocabulary with the reference's ordering (total order on the bit patterns,
+// last index wins ties); optional soft-cap written back to the logits first.
+__global__ void k_argmax(float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
+                         uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance) {
+  __shared__ unsigned long long sh[32];
+  const int64_t b = blockIdx.x;
+  unsigned long long best = 0;
+  for (int part = 0; part < parts; ++part) {
+    float* row = logits + ((int64_t)part * B + b) * Vp;
+    for (int64_t i = threadIdx.x; i < Vp; i += blockDim.x) {
+      float v = row[i];
+      if (softcap > 0.f) { v = softcap * tanh_f(v / softcap); row[i] = v; }
+      uint32_t bits = __float_as_uint(v);
+      uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+      unsigned long long p = ((unsigned long long)key << 32) | (uint32_t)(part * Vp + i);
+      best = p > best ? p : best;
+    }
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int o = 16; o; o >>= 1) {
+    unsigned long long w = __shfl_xor_sync(0xffffffffu, best, o);
+    best = w > best ? w : best;
+  }
+  if (lane == 0) sh[wid] = best;
+  __syncthreads();
+  if (wid == 0) {
+    best = lane < nw ? sh[lane] : 0ull;
+    for (int o = 16; o; o >>= 1) {
+      unsigned long long w = __shfl_xor_sync(0xffffffffu, best, o);
+      best = w > best ? w : best;
+    }
+    if (lane == 0) {
+      const uint32_t t = (uint32_t)(best & 0xFFFFFFFFull);
+      tokens[b] = t;
+      if (history) history[b * hist_ld + *count_dev] = t;
+    }
+  }
+}
+// after every row has used the counters: one more generated token, one more cached position
+__global__ void k_advance(int64_t* count_dev, int64_t* pos_dev) {
+  *count_dev += 1;
+  *pos_dev += 1;
+}
+
+__global__ void k_to_bf16(const float* x, int64_t n, __nv_bfloat16* out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(x[i]);
+}
+
+}  // namespace
+
+int k_launch_embed(cg_ctx* c, const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,
+                   int64_t vocab, int64_t M, int64_t H, float scale, float* out) {
+  if (M == 0) return CG_OK;
+  k_embed<<<(unsigned)M, 256, 0, c->core->stream>>>(tokens, tok_ld, tok_off, S, table, st, vocab, H, scale, out,
+                                                   c->core->dev_err);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rmsnorm(cg_ctx* c, const float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t M,
+                     int64_t H, void* out, int out_bf16) {
+  if (M == 0) return CG_OK;
+  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (out_bf16) k_rmsnorm<1><<<(unsigned)M, block, 0, c->core->stream>>>(x, ldx, gamma, eps, plus_one, H, out);
+  else k_rmsnorm<0><<<(unsigned)M, block, 0, c->core->stream>>>(x, ldx, gamma, eps, plus_one, H, out);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float eps, int plus_one, int64_t M, int64_t H,
+                         float* x) {
+  if (M == 0) return CG_OK;
+  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  k_rmsnorm<2><<<(unsigned)M, block, 0, c->core->stream>>>(y, H, gamma, eps, plus_one, H, x);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out) {
+  if (M == 0 || F == 0) return CG_OK;
+  dim3 grid((unsigned)std::min<int64_t>((F + 255) / 256, 64), (unsigned)M);
+  k_act_mul<<<grid, 256, 0, c->core->stream>>>(gu, F, act, out);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* cos_t, float* sin_t) {
+  const int64_t n = T * (d / 2);
+  if (n == 0) return CG_OK;
+  const float two_over_d = 2.0f / (float)d;
+  k_rope_tables<<<grid_for(n, 256), 256, 0, c->core->stream>>>(theta, T, d / 2, two_over_d, cos_t, sin_t);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
+  const int64_t warps = a.M * (a.nh + 2 * a.nkv);
+  if (warps == 0) return CG_OK;
+  const int block = 256;
+  const int64_t blocks = (warps * 32 + block - 1) / block;
+  k_rope_store<<<(unsigned)blocks, block, 0, c->core->stream>>>(a);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
+                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance) {
+  if (B == 0) return CG_OK;
+  k_argmax<<<(unsigned)B, 1024, 0, c->core->stream>>>(logits, B, Vp, parts, softcap, tokens, history, hist_ld, count_dev,
+                                                     pos_dev, advance);
+  CG_LAUNCHED(c);
+  if (advance) {
+    k_advance<<<1, 1, 0, c->core->stream>>>(count_dev, pos_dev);
+    CG_LAUNCHED(c);
+  }
+  return CG_OK;
+}
+
+int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out) {
+  if (n == 0) return CG_OK;
+  k_to_bf16<<<grid_for(n, 256), 256, 0, c->core->stream>>>(x, n, out);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+}  // namespace cg
+
+using namespace cg;
+
+// --------------------------------------------------------------- public fused entry points
+
+extern "C" {
+
+int32_t cg_fused_rmsnorm(cg_ctx* c, const cg_tensor* x, const cg_tensor* gamma, float eps, int32_t plus_one, cg_tensor** out) {
+  if (!c || !x || !gamma || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (x->tag != CG_F32 || gamma->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "rmsnorm wants F32 tensors");
+  if (x->rank < 1 || gamma->numel() != x->dims[x->rank - 1]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  Hold xc, gc, r;
+  CG_TRY(as_contiguous_f32(c, x, &xc.t));
+  CG_TRY(as_contiguous_f32(c, gamma, &gc.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, x->dims, x->rank, &r.t));
+  const int64_t H = x->dims[x->rank - 1];
+  const int64_t M = H ? x->numel() / H : 0;
+  if (M > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "too many rows");
+  CG_TRY(k_launch_rmsnorm(c, (const float*)xc.t->data(), H, (const float*)gc.t->data(), eps, plus_one, M, H, r.t->data(), 0));
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_fused_softmax(cg_ctx* c, const cg_tensor* x, float softcap, cg_tensor** out) {
+  if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "softmax wants an F32 tensor");
+  if (x->rank < 1) return fail(c, CG_ERR_SHAPE, "softmax of a rank-0 tensor");
+  Hold xc, r;
+  CG_TRY(as_contiguous_f32(c, x, &xc.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, x->dims, x->rank, &r.t));
+  const int64_t n = x->dims[x->rank - 1];
+  const int64_t rows = n ? x->numel() / n : 0;
+  if (rows > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "too many rows");
+  if (rows) {
+    const int block = n >= 2048 ? 512 : (n >= 256 ? 256 : 64);
+    k_softmax<<<(unsigned)rows, block, 0, c->core->stream>>>((const float*)xc.t->data(), n, softcap, (float*)r.t->data());
+    CG_LAUNCHED(c);
+  }
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_fused_act_mul(cg_ctx* c, const cg_tensor* gate, const cg_tensor* up, int32_t act, cg_tensor** out) {
+  if (!c || !gate || !up || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (gate->tag != CG_F32 || up->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "act_mul wants F32 tensors");
+  if (gate->rank != up->rank) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  for (int i = 0; i < gate->rank; ++i)
+    if (gate->dims[i] != up->dims[i]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  if (act != 0 && act != 1) return fail(c, CG_ERR_INVALID, "unknown activation");
+  Hold g, u, r;
+  CG_TRY(as_contiguous_f32(c, gate, &g.t));
+  CG_TRY(as_contiguous_f32(c, up, &u.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, gate->dims, gate->rank, &r.t));
+  const int64_t n = r.t->numel();
+  if (n) {
+    k_act_mul_f32<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)g.t->data(), (const float*)u.t->data(), n,
+                                                                act, (float*)r.t->data());
+    CG_LAUNCHED(c);
+  }
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_fused_rope(cg_ctx* c, const cg_tensor* x, float theta, int64_t pos0, cg_tensor** out) {
+  if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "rope wants an F32 tensor");
+  if (x->rank != 4 || (x->dims[3] & 1) || pos0 < 0) return fail(c, CG_ERR_SHAPE, "rope wants [b, heads, s, d] with even d");
+  const int64_t S = x->dims[2], d = x->dims[3], T = pos0 + S;
+  Hold xc, r, ct, sn;
+  CG_TRY(as_contiguous_f32(c, x, &xc.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, x->dims, x->rank, &r.t));
+  int64_t td[2] = {T, d / 2};
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &ct.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &sn.t));
+  CG_TRY(k_launch_rope_tables(c, theta, T, d, (float*)ct.t->data(), (float*)sn.t->data()));
+  const int64_t n = r.t->numel();
+  if (n) {
+    k_rope_apply<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)xc.t->data(), (const float*)ct.t->data(),
+                                                               (const float*)sn.t->data(), S, d, pos0, n,
+                                                               (float*)r.t->data());
+    CG_LAUNCHED(c);
+  }
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_linear(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, cg_tensor** out) {
+  if (!c || !x || !w || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (x->tag != CG_F32 || w->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "linear wants F32 tensors");
+  if (x->rank < 1 || w->rank != 2 || x->dims[x->rank - 1] != w->dims[1]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  const int64_t K = w->dims[1], N = w->dims[0];
+  const int64_t M = K ? x->numel() / K : 0;
+  int64_t od[CG_MAX_RANK];
+  for (int i = 0; i < x->rank; ++i) od[i] = x->dims[i];
+  od[x->rank - 1] = N;
+  Hold r;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, od, x->rank, &r.t));
+  if (r.t->numel() == 0) { *out = r.take(); return CG_OK; }
+  if (K == 0) {
+    CG_CUDA(c, cudaMemsetAsync(r.t->data(), 0, (size_t)r.t->numel() * 4, c->core->stream));
+    *out = r.take();
+    return CG_OK;
+  }
+  const bool tc = c->opt_gemm == 0 && w->storage == ST_BF16 && w->contiguous() && K % 8 == 0 &&
+                  ((uintptr_t)w->data() % 16 == 0);
+  if (tc) {
+    Hold xc, xb;
+    CG_TRY(as_contiguous(c, x, &xc.t));
+    const __nv_bfloat16* xp;
+    if (xc.t->storage == ST_BF16) {
+      xp = (const __nv_bfloat16*)xc.t->data();
+    } else {
+      int64_t xd[2] = {M, K};
+      CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xb.t));
+      CG_TRY(k_launch_to_bf16(c, (const float*)xc.t->data(), M * K, (__nv_bfloat16*)xb.t->data()));
+      xp = (const __nv_bfloat16*)xb.t->data();
+    }
+    CG_TRY(gemm_tc(c, xp, K, (const __nv_bfloat16*)w->data(), K, r.t->data(), N, nullptr, M, N, K, 0, 0, nullptr));
+  } else {
+    // [1, M, K] x [1, K, N] through strided views, like linear_b_param's transpose + reshape
+    Hold xc;
+    CG_TRY(as_contiguous(c, x, &xc.t));
+    Hold xv(new_view(xc.t)), wv(new_view(w)), rv(new_view(r.t));
+    xv.t->rank = 2; xv.t->dims[0] = M; xv.t->dims[1] = K; xv.t->strides[0] = K; xv.t->strides[1] = 1;
+    wv.t->rank = 2; wv.t->dims[0] = K; wv.t->dims[1] = N; wv.t->strides[0] = w->strides[1]; wv.t->strides[1] = w->strides[0];
+    rv.t->rank = 2; rv.t->dims[0] = M; rv.t->dims[1] = N; rv.t->strides[0] = N; rv.t->strides[1] = 1;
+    CG_TRY(gemm_simt(c, xv.t, wv.t, rv.t));
+  }
+  *out = r.take();
+  return CG_OK;
+}
+
+}  // extern "C"

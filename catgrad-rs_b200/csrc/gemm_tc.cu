@@ -1,0 +1,368 @@
+// gemm_tc.cu — bf16 GEMM on the Blackwell tensor cores: y[M,N] = x[M,K] w[N,K]^T.
+//
+// The weight is consumed as the checkpoints store it ([out, in], k unit-stride), so the
+// `transpose` + `reshape` of catgrad's linear layer (catgrad/src/stdlib/nn/mod.rs:174-199)
+// never touches memory.  The operands are swapped on the way into the instruction: a
+// 128-row tile of W is the MMA's M side and a tile of TN tokens its N side, so one
+// kernel serves decode (TN = 16, HBM-bound weight streaming with split-K) and prefill
+// (TN = 256, tensor-bound).
+//
+// Pipeline per CTA (192 threads, 1 CTA per SM):
+//   warp 0      one lane issues TMA loads (128B-swizzled [rows, 64] bf16 boxes) into a
+//               ring of STAGES shared-memory slots, signalled through mbarriers
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma (128 x TN x 16, f32 accumulate
+//               in TMEM) and commits slot releases / the final "accumulator ready"
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (lane = output feature, column =
+//               token) and store coalesced along the feature axis
+// Every mbarrier wait is bounded (about one second); on expiry the kernel raises the
+// context's error word, still frees its TMEM and returns.
+#include <cuda.h>
+
+#include "runtime.h"
+
+namespace cg {
+
+namespace {
+
+constexpr int BM = 128;       // W rows per CTA (MMA M)
+constexpr int BK = 64;        // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_BYTES = BM * BK * 2;
+
+struct TcArgs {
+  void* out;
+  const float* residual;
+  float* partial;
+  int64_t ldo;
+  int M, N, K;
+  int out_mode;  // 0 f32, 1 bf16, 2 f32 + residual
+  int kb_total, kb_per_split, splits;
+  int32_t* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait on an mbarrier phase.  Returns false (and raises *err) after ~1 s or once
+// another wait of this CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int32_t* err) {
+  uint32_t done = 0;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 0x3FF) == 0x3FF) {
+      if (*cta_abort) return false;
+      uint64_t now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 1000000000ull) break;
+    }
+  }
+  *cta_abort = 1;
+  *err = DEV_TIMEOUT;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a k-major, 128B-swizzled tile whose rows are 128
+// bytes: 8-row groups are 1024 bytes apart (SBO), LBO is unused for swizzled k-major.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                    // leading byte offset (ignored)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // descriptor version for this architecture
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands k-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int TN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs p) {
+  constexpr uint32_t B_BYTES = TN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t NCOLS = TN < 32 ? 32 : TN;  // TMEM columns: power of two >= 32
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  const uint32_t bar_accum = bars + 16 * STAGES;
+  uint8_t* gen = smem_raw + (base - raw);
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen + STAGES * STAGE_BYTES + 16 * STAGES + 8);
+  volatile int* cta_abort = (volatile int*)(gen + STAGES * STAGE_BYTES + 16 * STAGES + 12);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * TN, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  const int nkb = kb1 - kb0;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bars + 8 * s, 1);             // full[s]: producer's expect_tx arrival + bytes
+      mbar_init(bars + 8 * (STAGES + s), 1);  // empty[s]: one tcgen05.commit
+    }
+    mbar_init(bar_accum, 1);
+    *cta_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                 "r"(NCOLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && nkb > 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
+        const uint32_t full = bars + 8 * s;
+        mbar_expect_tx(full, STAGE_BYTES);
+        const uint32_t a = base + s * STAGE_BYTES;
+        const int k = (kb0 + i) * BK;
+        tma_load_2d(a, &map_w, k, n0, full);
+        tma_load_2d(a + A_BYTES, &map_x, k, m0, full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkb > 0) {
+      constexpr uint32_t idesc = umma_idesc(TN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(bars + 8 * s, ph, cta_abort, p.err);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = base + s * STAGE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          const uint64_t da = umma_desc(a + kk * UMMA_K * 2);
+          const uint64_t db = umma_desc(a + A_BYTES + kk * UMMA_K * 2);
+          umma_bf16(tmem_acc, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(bars + 8 * (STAGES + s));  // slot reusable once these MMAs have read it
+      }
+      if (ok) umma_commit(bar_accum);
+    }
+  } else if (nkb > 0) {
+    // TMEM lanes a warp may read: 32 * (warp id mod 4)
+    const int q = warp & 3;
+    const int n = n0 + q * 32 + lane;
+    const bool ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        if (m0 + c0 >= p.M) break;
+        uint32_t v[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m >= p.M) break;
+            const float acc = __uint_as_float(v[j]);
+            if (p.splits > 1) {
+              p.partial[((int64_t)split * p.M + m) * p.N + n] = acc;
+            } else if (p.out_mode == 0) {
+              ((float*)p.out)[(int64_t)m * p.ldo + n] = acc;
+            } else if (p.out_mode == 1) {
+              ((__nv_bfloat16*)p.out)[(int64_t)m * p.ldo + n] = __float2bfloat16_rn(acc);
+            } else {
+              ((float*)p.out)[(int64_t)m * p.ldo + n] = acc + p.residual[(int64_t)m * p.ldo + n];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(NCOLS) : "memory");
+  }
+}
+
+// out = sum over splits of partial (+ residual), in the output precision.
+__global__ void k_splitk_reduce(const float* partial, int splits, int64_t M, int64_t N, void* out, int64_t ldo,
+                                const float* residual, int out_mode) {
+  const int64_t total = M * N;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(int64_t)s * total + i];
+    const int64_t m = i / N, n = i - m * N;
+    const int64_t o = m * ldo + n;
+    if (out_mode == 0) ((float*)out)[o] = acc;
+    else if (out_mode == 1) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(acc);
+    else ((float*)out)[o] = acc + residual[o];
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_map(cg_ctx* c, CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  if (!c->encode_tiled) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return fail(c, CG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    c->encode_tiled = fn;
+  }
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstr[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = ((EncodeTiledFn)c->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim,
+                                                gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, CG_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return CG_OK;
+}
+
+template <int TN, int STAGES>
+int launch(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid) {
+  constexpr size_t smem = (size_t)STAGES * (A_BYTES + TN * BK * 2) + 1024 + 16 * STAGES + 64;
+  static bool configured = false;  // per instantiation; the attribute is per function and device-wide
+  if (!configured) {
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  k_gemm_tc<TN, STAGES><<<grid, 192, smem, c->core->stream>>>(mw, mx, a);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int pick_tn(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+}  // namespace
+
+int gemm_tc_pick_splits(int64_t M, int64_t N, int64_t K) {
+  const int tn = pick_tn(M);
+  const int64_t tiles = ((N + BM - 1) / BM) * ((M + tn - 1) / tn);
+  const int64_t kb = (K + BK - 1) / BK;
+  if (tiles >= 148 || kb < 8) return 1;
+  int64_t s = (2 * 148 + tiles - 1) / tiles;
+  s = std::min<int64_t>(s, kb / 4);
+  s = std::min<int64_t>(s, 32);
+  return (int)std::max<int64_t>(s, 1);
+}
+
+int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, void* out, int64_t ldo,
+            const float* residual, int64_t M, int64_t N, int64_t K, int out_mode, int splits, float* workspace) {
+  if (M <= 0 || N <= 0) return CG_OK;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+    return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: k and leading dimensions must be multiples of 8, bases 16-byte aligned");
+  if (M > 2147483647ll / 2 || N > 2147483647ll / 2) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: problem too large");
+  const int tn = pick_tn(M);
+  const int kb_total = (int)((K + BK - 1) / BK);
+  if (splits <= 0) splits = gemm_tc_pick_splits(M, N, K);
+  splits = std::min(splits, kb_total);
+  int kb_per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per - 1) / kb_per;  // no empty slices
+
+  Hold ws;
+  if (splits > 1 && !workspace) {
+    int64_t n = (int64_t)splits * M * N;
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &ws.t));
+    workspace = (float*)ws.t->data();
+  }
+
+  CUtensorMap mw, mx;
+  CG_TRY(make_map(c, &mw, w, N, K, ldw, BM));
+  CG_TRY(make_map(c, &mx, x, M, K, ldx, tn));
+
+  TcArgs a;
+  a.out = out;
+  a.residual = residual;
+  a.partial = workspace;
+  a.ldo = ldo;
+  a.M = (int)M;
+  a.N = (int)N;
+  a.K = (int)K;
+  a.out_mode = out_mode;
+  a.kb_total = kb_total;
+  a.kb_per_split = kb_per;
+  a.splits = splits;
+  a.err = c->core->dev_err;
+  dim3 grid((unsigned)((N + BM - 1) / BM), (unsigned)((M + tn - 1) / tn), (unsigned)splits);
+  if (grid.y > 65535) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: too many token tiles");
+  switch (tn) {
+    case 16: CG_TRY((launch<16, 10>(c, mw, mx, a, grid))); break;
+    case 32: CG_TRY((launch<32, 10>(c, mw, mx, a, grid))); break;
+    case 64: CG_TRY((launch<64, 8>(c, mw, mx, a, grid))); break;
+    case 128: CG_TRY((launch<128, 6>(c, mw, mx, a, grid))); break;
+    default: CG_TRY((launch<256, 4>(c, mw, mx, a, grid))); break;
+  }
+  if (splits > 1) {
+    k_splitk_reduce<<<grid_for(M * N, 256), 256, 0, c->core->stream>>>(workspace, splits, M, N, out, ldo, residual,
+                                                                     out_mode);
+    CG_LAUNCHED(c);
+  }
+  return CG_OK;
+}
+
+}  // namespace cg

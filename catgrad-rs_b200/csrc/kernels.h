@@ -1,0 +1,79 @@
+// kernels.h — launchers of the fused kernels shared by the public fused entry points and
+// the decoder runner.  All pointers are device pointers; all arrays are contiguous
+// row-major unless a leading dimension is given.
+#pragma once
+
+#include "runtime.h"
+
+namespace cg {
+
+// x[m, :] = table[tok(m), :] * scale (table f32 or bf16), where row m = b * S + s reads
+// tokens[b * tok_ld + tok_off + s]: a window of S positions out of a [B, tok_ld] id matrix.
+int k_launch_embed(cg_ctx* c, const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table,
+                   int table_storage, int64_t vocab, int64_t M, int64_t H, float scale, float* out);
+
+// RMSNorm of each row of x [M, H] (row stride ldx): out = x / sqrt(mean(x^2) + eps) * g, g = gamma or 1 + gamma.
+// out_bf16 selects the output element type (bf16 feeds the tensor-core GEMMs).
+int k_launch_rmsnorm(cg_ctx* c, const float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t M,
+                     int64_t H, void* out, int out_bf16);
+// In-place residual update with a normalised addend: x += rmsnorm(y) (post-norm layers).
+int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float eps, int plus_one, int64_t M, int64_t H,
+                         float* x);
+
+// act(gu[m, 0:F]) * gu[m, F:2F] -> bf16 [M, F]; act 0 = silu, 1 = tanh-gelu.
+int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out);
+
+// Rotary tables exactly as the reference builds them: cos/sin [T, d/2] f32.
+int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* cos_t, float* sin_t);
+
+struct RopeStoreArgs {
+  const float* qkv;        // [M, (nh + 2 nkv) d]
+  const float* cos_t;      // [T, d/2]
+  const float* sin_t;
+  const float* q_gamma;    // optional per-head norm weights [d] (null = none)
+  const float* k_gamma;
+  float norm_eps;
+  int norm_plus_one;
+  __nv_bfloat16* q_out;    // [M, nh d]
+  __nv_bfloat16* k_cache;  // [B, nkv, Tmax, d]
+  __nv_bfloat16* v_cache;
+  int64_t M, S;            // M = B * S tokens; token m is row m / S at position pos0 + m % S
+  int64_t pos0, Tmax;
+  const int64_t* pos_dev;  // when non-null, pos0 is read from device memory instead
+  int nh, nkv, d;
+};
+// Split qkv, optionally normalise q/k per head, rotate q and k, write q (bf16) and append k, v
+// to the cache.
+int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a);
+
+struct AttnArgs {
+  const __nv_bfloat16* q;        // [B * S, nh d]
+  const __nv_bfloat16* k_cache;  // [B, nkv, Tmax, d]
+  const __nv_bfloat16* v_cache;
+  __nv_bfloat16* out;            // [B * S, nh d]
+  int64_t B, S, pos0, Tmax;
+  const int64_t* pos_dev;        // decode only: when non-null, pos0 is read from device memory
+  int nh, nkv, d;
+  int64_t window;                // 0 = none
+  float softcap;                 // 0 = none
+  float* scratch;                // decode only: split partials, see attn_decode_scratch_floats
+};
+// Causal (optionally windowed / soft-capped) attention of S new tokens per row against cache
+// positions [0, pos0 + S).  Tensor-core flash kernel.
+int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a);
+// One new token per row (S == 1): split-KV streaming kernel + combine.
+int k_launch_attn_decode(cg_ctx* c, const AttnArgs& a);
+int64_t attn_decode_scratch_floats(int64_t B, int nh, int d);
+
+// tokens[b] = argmax over the vocabulary with the reference's tie rule (last index); optional
+// soft-cap applied to the logits in place first.  The logits are `parts` vocabulary slices of
+// Vp entries laid out [parts, B, Vp] (parts = 1: plain [B, V]).  Also appends the token to
+// history[b * hist_ld + n] where n = *count_dev (a device counter) and, if advance != 0,
+// increments *count_dev and *pos_dev afterwards.
+int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
+                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance);
+
+// f32 -> bf16 rows (ld in elements for the source)
+int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out);
+
+}  // namespace cg

@@ -1,0 +1,177 @@
+// runtime.h — internal definitions shared by the translation units of libcatgrad_cuda.so:
+// context (stream, caching allocator, device error word), reference-counted tensor handles
+// with shape/stride views, and the helpers every entry point uses.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/catgrad_cuda.h"
+
+namespace cg {
+
+enum Storage : int32_t { ST_F32 = 0, ST_U32 = 1, ST_BF16 = 2 };
+
+inline size_t storage_bytes(int st) { return st == ST_BF16 ? 2 : 4; }
+
+// Codes a kernel may leave in the context's device error word.
+enum DevErr : int32_t { DEV_OK = 0, DEV_INDEX = 1, DEV_TIMEOUT = 2 };
+
+struct Core;
+
+// One device allocation handed out by the caching allocator.
+struct Buffer {
+  std::shared_ptr<Core> core;
+  void* ptr = nullptr;
+  size_t bytes = 0;   // size of the underlying block
+  bool owned = true;  // false: memory belongs to someone else (never freed here)
+  ~Buffer();
+};
+
+// The part of a context that tensors keep alive: device, stream, allocator.
+struct Core {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  std::mutex mu;
+  std::multimap<size_t, void*> free_blocks;  // size -> ptr, reusable at once: one stream
+  int64_t reserved = 0;                      // bytes obtained from cudaMalloc and not returned
+  int32_t* dev_err = nullptr;                // device error word (DevErr)
+  ~Core();
+  void* alloc(size_t bytes, size_t* got);
+  void recycle(void* p, size_t bytes);
+  void trim();
+};
+
+}  // namespace cg
+
+struct cg_ctx {
+  std::shared_ptr<cg::Core> core;
+  int precision = CG_PREC_F32;
+  std::string err;
+  int64_t launches = 0;
+  int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
+  void* comm = nullptr;   // ncclComm_t
+  int comm_rank = 0, comm_world = 1;
+  // host function pointer of cuTensorMapEncodeTiled, resolved on first use
+  void* encode_tiled = nullptr;
+};
+
+struct cg_tensor {
+  std::atomic<int> rc{1};
+  cg_ctx* ctx = nullptr;
+  int tag = CG_F32;            // the interpreter's dtype tag
+  int storage = cg::ST_F32;    // how elements are stored
+  int rank = 0;
+  int64_t dims[CG_MAX_RANK] = {0};
+  int64_t strides[CG_MAX_RANK] = {0};  // in elements
+  int64_t offset = 0;                  // in elements
+  std::shared_ptr<cg::Buffer> buf;
+
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < rank; ++i) n *= dims[i];
+    return n;
+  }
+  bool contiguous() const {
+    int64_t s = 1;
+    for (int i = rank - 1; i >= 0; --i) {
+      if (dims[i] != 1 && strides[i] != s) return false;
+      s *= dims[i];
+    }
+    return true;
+  }
+  size_t esize() const { return cg::storage_bytes(storage); }
+  void* data() const { return (char*)buf->ptr + (size_t)offset * esize(); }
+};
+
+namespace cg {
+
+int fail(cg_ctx* c, int code, const std::string& msg);
+int cuda_fail(cg_ctx* c, cudaError_t e, const char* what);
+
+#define CG_CUDA(ctx, call)                                   \
+  do {                                                       \
+    cudaError_t e__ = (call);                                \
+    if (e__ != cudaSuccess) return cg::cuda_fail(ctx, e__, #call); \
+  } while (0)
+
+// After a kernel launch: count it and surface launch errors.
+#define CG_LAUNCHED(ctx)                                              \
+  do {                                                                \
+    (ctx)->launches++;                                                \
+    cudaError_t e__ = cudaGetLastError();                             \
+    if (e__ != cudaSuccess) return cg::cuda_fail(ctx, e__, "kernel launch"); \
+  } while (0)
+
+#define CG_TRY(expr)            \
+  do {                          \
+    int st__ = (expr);          \
+    if (st__ != CG_OK) return st__; \
+  } while (0)
+
+// New contiguous tensor with fresh storage.
+int new_tensor(cg_ctx* c, int tag, int storage, const int64_t* dims, int rank, cg_tensor** out);
+// New handle sharing t's buffer (same view); caller edits dims/strides/offset.
+cg_tensor* new_view(const cg_tensor* t);
+void release(cg_tensor* t);
+
+// RAII holder for temporaries inside entry points.
+struct Hold {
+  cg_tensor* t = nullptr;
+  Hold() = default;
+  explicit Hold(cg_tensor* p) : t(p) {}
+  Hold(const Hold&) = delete;
+  Hold& operator=(const Hold&) = delete;
+  ~Hold() { if (t) release(t); }
+  cg_tensor* take() { cg_tensor* p = t; t = nullptr; return p; }
+};
+
+// A contiguous tensor equal to x: x itself (retained) when already contiguous.
+int as_contiguous(cg_ctx* c, const cg_tensor* x, cg_tensor** out);
+// Like as_contiguous but also widens bf16 storage to f32.
+int as_contiguous_f32(cg_ctx* c, const cg_tensor* x, cg_tensor** out);
+
+// Up to three operands sharing one iteration space, passed to kernels by value.
+struct Iter {
+  int rank;
+  int64_t dims[CG_MAX_RANK];
+  int64_t s0[CG_MAX_RANK], s1[CG_MAX_RANK], s2[CG_MAX_RANK];
+};
+// Build an Iter from shapes/strides, merging adjacent dims that are jointly contiguous
+// in every operand and dropping unit dims.  Unused operands pass nullptr strides.
+Iter make_iter(int rank, const int64_t* dims, const int64_t* s0, const int64_t* s1, const int64_t* s2);
+
+inline int grid_for(int64_t n, int block, int max_blocks = 148 * 16) {
+  int64_t g = (n + block - 1) / block;
+  if (g < 1) g = 1;
+  if (g > max_blocks) g = max_blocks;
+  return (int)g;
+}
+
+// ---- entry points implemented in other translation units, used across them ----------
+
+// y[M,N] = x[M,K] w[N,K]^T on the tcgen05 pipeline.  x, w bf16 row-major (ld in elements);
+// out_mode 0: f32 store, 1: bf16 store, 2: f32 out = acc + residual (residual may alias out).
+// splits <= 0 lets the launcher choose.  `workspace` must hold splits*M*N floats when
+// splits > 1 (pass nullptr to have it allocated from the context).
+int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,
+            void* out, int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K,
+            int out_mode, int splits, float* workspace);
+// How many split-K slices gemm_tc would pick for this problem.
+int gemm_tc_pick_splits(int64_t M, int64_t N, int64_t K);
+
+// Generic strided f32 / u32 batched GEMM on CUDA cores (parity path).
+int gemm_simt(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, cg_tensor* out);
+
+}  // namespace cg

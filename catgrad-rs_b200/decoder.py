@@ -1,0 +1,130 @@
+"""The fused, KV-cached greedy runner over libcatgrad_cuda.so (cg_decoder_* entry points).
+
+It does what the reference's example driver does (catgrad-llm/examples/llama/main.rs:118-169)
+with the model graph of catgrad-llm/src/models/llama.rs, but as fused kernels over a device
+KV cache instead of one full forward per generated token.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from .backend import CudaBackend, TaggedTensor, U32, _c_vp
+
+
+class DecoderConfig(C.Structure):
+    """Mirror of `cg_decoder_config` (include/catgrad_cuda.h)."""
+    _fields_ = [
+        ("arch", C.c_int32), ("num_layers", C.c_int32), ("hidden", C.c_int32), ("n_heads", C.c_int32),
+        ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32),
+        ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("tie_embeddings", C.c_int32),
+        ("max_seq", C.c_int32), ("max_batch", C.c_int32),
+        ("qk_norm", C.c_int32), ("act", C.c_int32), ("norm_plus_one", C.c_int32), ("post_norms", C.c_int32),
+        ("embed_scale", C.c_float), ("attn_softcap", C.c_float), ("final_softcap", C.c_float),
+        ("sliding_window", C.c_int32), ("window_every", C.c_int32),
+        ("n_experts", C.c_int32), ("top_k", C.c_int32), ("moe_ffn", C.c_int32), ("norm_topk", C.c_int32),
+        ("tp_rank", C.c_int32), ("tp_world", C.c_int32),
+    ]
+
+
+class Decoder:
+    def __init__(self, backend: CudaBackend, cfg, max_seq: int, max_batch: int, tp_rank: int = 0, tp_world: int = 1,
+                 **switches):
+        self.B = backend
+        L = backend._lib
+        vp, i32 = _c_vp, C.c_int32
+        out = C.POINTER(vp)
+        for name, args in [
+            ("cg_decoder_create", [vp, C.POINTER(DecoderConfig), out]),
+            ("cg_decoder_destroy", [vp]),
+            ("cg_decoder_set_param", [vp, C.c_char_p, vp]),
+            ("cg_decoder_finalize", [vp]),
+            ("cg_decoder_reset", [vp]),
+            ("cg_decoder_prefill", [vp, vp, out]),
+            ("cg_decoder_decode", [vp, i32, out]),
+            ("cg_decoder_step_with", [vp, vp, out]),
+            ("cg_decoder_tokens", [vp, out]),
+            ("cg_decoder_generate", [vp, vp, i32, i32, i32, vp]),
+        ]:
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = i32
+        c = DecoderConfig()
+        c.arch = 0
+        c.num_layers = cfg.num_hidden_layers
+        c.hidden = cfg.hidden_size
+        c.n_heads = cfg.num_attention_heads
+        c.n_kv_heads = cfg.num_key_value_heads
+        c.head_dim = cfg.get_head_dim()
+        c.ffn = cfg.intermediate_size
+        c.vocab = cfg.vocab_size
+        c.rms_eps = cfg.rms_norm_eps
+        c.rope_theta = cfg.rope_theta
+        c.tie_embeddings = int(cfg.tie_word_embeddings)
+        c.max_seq = max_seq
+        c.max_batch = max_batch
+        c.tp_rank = tp_rank
+        c.tp_world = tp_world
+        for k, v in switches.items():
+            setattr(c, k, v)
+        self.cfg = c
+        h = vp()
+        backend._check(L.cg_decoder_create(backend._ctx, C.byref(c), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if self._h is not None:
+            self.B._lib.cg_decoder_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_param(self, name: str, t: TaggedTensor):
+        self.B._check(self.B._lib.cg_decoder_set_param(self._h, name.encode(), t._h))
+
+    def load(self, named_arrays):
+        """Upload (name, f32 array) pairs one at a time and hand them to the decoder."""
+        for name, w in named_arrays:
+            self.set_param(name, self.B.from_numpy(w))
+        self.finalize()
+
+    def finalize(self):
+        self.B._check(self.B._lib.cg_decoder_finalize(self._h))
+
+    def reset(self):
+        self.B._check(self.B._lib.cg_decoder_reset(self._h))
+
+    def _maybe_logits(self, fn, *args, want_logits=False):
+        if want_logits:
+            h = _c_vp()
+            self.B._check(fn(self._h, *args, C.byref(h)))
+            return self.B._wrap(h)
+        self.B._check(fn(self._h, *args, None))
+        return None
+
+    def prefill(self, tokens: TaggedTensor, want_logits=False):
+        return self._maybe_logits(self.B._lib.cg_decoder_prefill, tokens._h, want_logits=want_logits)
+
+    def decode(self, steps: int, want_logits=False):
+        return self._maybe_logits(self.B._lib.cg_decoder_decode, int(steps), want_logits=want_logits)
+
+    def step_with(self, tokens: TaggedTensor, want_logits=False):
+        return self._maybe_logits(self.B._lib.cg_decoder_step_with, tokens._h, want_logits=want_logits)
+
+    def tokens(self) -> np.ndarray:
+        h = _c_vp()
+        self.B._check(self.B._lib.cg_decoder_tokens(self._h, C.byref(h)))
+        return self.B.to_numpy(self.B._wrap(h, U32))
+
+    def generate(self, prompt: np.ndarray, n_decode: int) -> np.ndarray:
+        """Host buffers in, host buffers out: [B, S] ids -> [B, 1 + n_decode] greedy ids."""
+        p = np.ascontiguousarray(prompt, dtype=np.uint32)
+        b, s = p.shape
+        out = np.empty((b, 1 + n_decode), dtype=np.uint32)
+        self.B._check(self.B._lib.cg_decoder_generate(self._h, p.ctypes.data, b, s, int(n_decode), out.ctypes.data))
+        return out

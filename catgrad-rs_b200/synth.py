@@ -1,0 +1,109 @@
+"""Seeded synthetic checkpoints and prompts.
+
+The reference downloads Hugging Face checkpoints at run time
+(catgrad-llm/src/utils.rs:104-146); none exist offline, so every configuration is run on
+random weights of the right shapes: each 2-D parameter ~ N(0, 0.02^2) drawn from
+numpy.random.Generator(PCG64(seed)) in sorted Hugging Face name order, norm gains = 1,
+token ids uniform in [0, V).  The same host arrays feed the checker and the GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass
+class ModelConfig:
+    """Shape of a Llama-family decoder (field names of catgrad-llm/src/legacy/models/utils.rs:52-112)."""
+    name: str
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    vocab_size: int
+    head_dim: int = 0
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    tie_word_embeddings: bool = False
+    dtype: str = "f32"
+    extras: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if not self.head_dim:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    def get_head_dim(self) -> int:
+        return self.head_dim
+
+
+# BASELINE configurations (shapes only; weights are synthetic)
+TINY_LLAMA = ModelConfig("tiny-llama-f32", 256, 688, 2, 4, 2, 32000, rms_norm_eps=1e-5, rope_theta=10000.0,
+                         tie_word_embeddings=False, dtype="f32")
+LLAMA_32_1B = ModelConfig("llama-3.2-1b-shape", 2048, 8192, 16, 32, 8, 128256, rms_norm_eps=1e-5,
+                          rope_theta=500000.0, tie_word_embeddings=True, dtype="bf16")
+LLAMA_3_8B = ModelConfig("llama-3-8b-shape", 4096, 14336, 32, 32, 8, 128256, rms_norm_eps=1e-5,
+                         rope_theta=500000.0, tie_word_embeddings=False, dtype="bf16")
+
+
+def param_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
+    """Hugging Face tensor names and shapes of a Llama checkpoint (all weights [out, in])."""
+    H, F, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nh, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    shapes = {"model.embed_tokens.weight": (cfg.vocab_size, H), "model.norm.weight": (H,)}
+    if not cfg.tie_word_embeddings:
+        shapes["lm_head.weight"] = (cfg.vocab_size, H)
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        shapes[p + "input_layernorm.weight"] = (H,)
+        shapes[p + "post_attention_layernorm.weight"] = (H,)
+        shapes[p + "self_attn.q_proj.weight"] = (nh * d, H)
+        shapes[p + "self_attn.k_proj.weight"] = (nkv * d, H)
+        shapes[p + "self_attn.v_proj.weight"] = (nkv * d, H)
+        shapes[p + "self_attn.o_proj.weight"] = (H, nh * d)
+        shapes[p + "mlp.gate_proj.weight"] = (F, H)
+        shapes[p + "mlp.up_proj.weight"] = (F, H)
+        shapes[p + "mlp.down_proj.weight"] = (H, F)
+    return shapes
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """Round f32 to the nearest bf16 (ties to even), returned as f32."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    rounded = (u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) & np.uint32(0xFFFF0000)
+    return rounded.view(np.float32)
+
+
+def make_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02):
+    """Yield (name, f32 array) in sorted name order.  bf16 configurations get weights already
+    rounded to bf16 so the f32 checker and the bf16 device copy hold the same numbers."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    shapes = param_shapes(cfg)
+    for name in sorted(shapes):
+        shp = shapes[name]
+        if len(shp) == 1:
+            w = np.ones(shp, dtype=np.float32)
+        else:
+            w = rng.standard_normal(shp, dtype=np.float32) * np.float32(std)
+            if cfg.dtype == "bf16":
+                w = bf16_round(w)
+        yield name, w
+
+
+def make_tokens(cfg: ModelConfig, batch: int, seq: int, seed: int = 1) -> np.ndarray:
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return rng.integers(0, cfg.vocab_size, size=(batch, seq), dtype=np.int64).astype(np.uint32)
+
+
+def linear_params_per_token(cfg: ModelConfig) -> int:
+    """Weights multiplied per token: every linear layer including the LM head, excluding the
+    embedding gather."""
+    H, F, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nh, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    per_layer = H * (nh * d) + 2 * H * (nkv * d) + (nh * d) * H + 3 * H * F
+    return cfg.num_hidden_layers * per_layer + cfg.vocab_size * H
+
+
+def kv_bytes_per_token(cfg: ModelConfig, elem_bytes: int = 2) -> int:
+    return 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * elem_bytes
