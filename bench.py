@@ -1,0 +1,311 @@
+"""Benchmark of the hot path: greedy generation on a Llama-3.2-1B-shaped decoder.
+
+One "step" is one whole job on synthetic data: prefill of B x PROMPT token ids followed by
+DECODE greedy steps, for all B rows.  The metric is tokens per second over prompt and
+generated tokens.  `value` is timed on the device with the token ids already resident in
+HBM; `e2e` is the same job through the host-buffer entry point (ids copied host->device,
+every step's tokens read back device->host).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torchrun, one rank per GPU; the model is tensor-parallel over the N
+ranks (NCCL all-reduce after the two row-split projections of every layer).
+
+`--impl reference` times the CPU restatement of the reference's ndarray backend running the
+reference's own op stream (one full forward per generated token, no KV cache) on the host
+cores, on a bounded sample of the same job.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode+prefill tok/s, Llama-3.2-1B shape"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples every 200 ms while a timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                c = [x.strip() for x in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    sm.append(float(c[1]))
+                    mx.append(float(c[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def reference_job_seconds(t_forward: float, prompt: int, decode: int, batch: int) -> float:
+    """Cost of the whole job on the reference's driver from one measured forward of `prompt`
+    tokens: every generated token is a full forward over all tokens so far
+    (catgrad-llm/examples/llama/main.rs:118-127), rows one at a time (the graphs are batch-1).
+    Forward cost is taken as linear in the length (the linear layers dominate)."""
+    lengths = [prompt + t for t in range(decode + 1)]
+    return batch * sum(t_forward * n / prompt for n in lengths)
+
+
+def run_reference_sample(cg, cfg, prompt_len: int, threads: int = 0):
+    """One full forward of one row through the reference op stream on the CPU checker."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "liboracle.so")
+    if not os.path.exists(path):
+        subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle")])
+    lib = ctypes.CDLL(path)
+    lib.cgo_ctx_create.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]
+    lib.cgo_ctx_threads.argtypes = [ctypes.c_void_p]
+    ctx = ctypes.c_void_p()
+    assert lib.cgo_ctx_create(threads, ctypes.byref(ctx)) == 0
+    O = cg.TraitBackend(lib, "cgo_", ctx)
+    cores = int(lib.cgo_ctx_threads(ctx))
+    params = {n: O.from_numpy(w) for n, w in cg.synth.make_weights(cfg, 0)}
+    ids = cg.synth.make_tokens(cfg, 1, prompt_len, seed=1)
+
+    def forward():
+        t0 = time.perf_counter()
+        y = cg.graphs.llama.forward(O, cfg, params, O.from_numpy(ids), prompt_len)
+        O.to_vec(y)
+        return time.perf_counter() - t0
+
+    return forward, cores
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="a 4-layer model of the same widths (profiling captures)")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours" and not args.small:
+        args.warmup = 3
+
+    cg = importlib.import_module("catgrad-rs_b200")
+    synth = cg.synth
+    import dataclasses
+    cfg = synth.LLAMA_32_1B
+    if args.small:
+        cfg = dataclasses.replace(cfg, name=cfg.name + "-4layer", num_hidden_layers=4)
+    B, S, T = args.batch, args.prompt, args.decode
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = f"{cfg.name} bf16, batch {B}, prompt {S}, {T} greedy decode steps"
+    tokens_per_job = B * (S + T)
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        forward, cores = run_reference_sample(cg, cfg, S)
+        for _ in range(max(args.warmup, 0)):
+            forward()
+        ts = [forward() for _ in range(max(args.steps, 1))]
+        t_fwd = float(np.mean(ts))
+        job = reference_job_seconds(t_fwd, S, T, B)
+        val = tokens_per_job / job
+        sample = (f"one full forward of 1 of {B} rows at {S} tokens per step ({t_fwd:.2f} s); the job "
+                  f"({B} rows x {T + 1} forwards of {S}..{S + T} tokens, no KV cache) is extrapolated linearly in length; "
+                  f"the reference's own ndarray build is single-threaded, this port uses {cores} threads")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": job * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": "cpu"},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # a named stream shared with torch, so torch.cuda.Event brackets the library's work
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    C = cg.CudaBackend(local, cg.PREC_BF16, stream=tstream.cuda_stream)
+    if world > 1:
+        import ctypes
+        L = C._lib
+        n = L.cg_comm_id_size()
+        buf = torch.zeros(n, dtype=torch.uint8)
+        if rank == 0:
+            raw = (ctypes.c_uint8 * n)()
+            assert L.cg_comm_make_id(raw) == 0
+            buf = torch.tensor(list(raw), dtype=torch.uint8)
+        buf = buf.cuda()
+        dist.broadcast(buf, 0)
+        raw = (ctypes.c_uint8 * n)(*buf.cpu().tolist())
+        L.cg_comm_init.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32]
+        C._check(L.cg_comm_init(C._ctx, raw, rank, world))
+
+    dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=B, tp_rank=rank, tp_world=world)
+    dec.load(synth.make_weights(cfg, 0))
+    prompt = synth.make_tokens(cfg, B, S, seed=1)
+    prompt_dev = C.from_numpy(prompt)
+    C.sync()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def job_device():
+        dec.prefill(prompt_dev)
+        dec.decode(T)
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        job_device()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = C.launch_count()
+    ms_total = timed(job_device, args.steps)
+    launches = C.launch_count() - launches0
+    # the host-buffer path: same job through cg_decoder_generate
+    out_tokens = None
+
+    def job_host():
+        nonlocal out_tokens
+        out_tokens = dec.generate(prompt, T)
+
+    job_host()
+    ms_e2e = timed(job_host, args.steps)
+    clocks = sampler.stop()
+
+    # phase split and the kernel-level roofline, measured live
+    ms_prefill = timed(lambda: dec.prefill(prompt_dev), args.steps) / args.steps
+    dec.prefill(prompt_dev)
+    dec.decode(1)
+    ms_decode = timed(lambda: dec.decode(T - 1), 1) / max(T - 1, 1)
+    gemm_ms, gemm_launches = dec.time_gemms(B, 20)
+    peak, peak_kind = measured_peaks()
+    weight_bytes = 2 * synth.linear_params_per_token(cfg) / world
+    kv_bytes = B * synth.kv_bytes_per_token(cfg) * (S + T / 2) / world
+    achieved = weight_bytes / (gemm_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath) and world == 1 and not args.small:
+        traffic = json.load(open(tpath)).get("decode_gemm_sweep_dram_bytes")
+
+    value = tokens_per_job * args.steps / (ms_total * 1e-3)
+    e2e = tokens_per_job * args.steps / (ms_e2e * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": f"tp{world}",
+                   "l2": "inputs larger than L2: every decode step streams the full weight set "
+                         f"({weight_bytes / 1e9:.2f} GB per GPU) plus the KV cache",
+                   "generator": f"numpy {np.__version__} PCG64, weights seed 0 N(0,0.02) rounded to bf16, ids seed 1"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(prompt.nbytes),
+                "d2h_bytes_per_step": int(B * (T + 1) * 4)},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "k_gemm_tc<16,10> + k_splitk_reduce: all weight-streaming GEMMs of one decode step",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                     "traffic": traffic, "algorithmic_bytes_per_sweep": weight_bytes, "launches_per_sweep": gemm_launches,
+                     "ms_per_sweep": gemm_ms},
+        "phases": {"prefill_ms": ms_prefill, "prefill_tok_s": B * S / (ms_prefill * 1e-3),
+                   "decode_ms_per_step": ms_decode, "decode_tok_s": B / (ms_decode * 1e-3),
+                   "decode_step_hbm_floor_ms": (weight_bytes + kv_bytes) / (peak * 1e9) * 1e3,
+                   "decode_step_frac_of_hbm_roofline": (weight_bytes + kv_bytes) / (peak * 1e9) * 1e3 / ms_decode},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        forward, cores = run_reference_sample(cg, dataclasses.replace(cfg, dtype="bf16"), S)
+        t_fwd = forward()
+        job = reference_job_seconds(t_fwd, S, T, B)
+        line["cpu_baseline"] = {
+            "value": tokens_per_job / job, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"one full forward of 1 of {B} rows at {S} tokens ({t_fwd:.2f} s) through the reference op stream on the "
+                      f"CPU restatement; the job ({B} rows x {T + 1} full forwards, no KV cache) extrapolated linearly in length"}
+    if rank == 0:
+        print(json.dumps(line))
+    dec.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -547,6 +547,41 @@ int32_t cg_decoder_step_with(cg_decoder* D, const cg_tensor* tokens, cg_tensor**
   return logits_copy(D, logits_out);
 }
 
+int32_t cg_decoder_time_gemms(cg_decoder* D, int32_t batch, int32_t iters, float* ms_per_sweep, int32_t* launches_per_sweep) {
+  if (!D || !ms_per_sweep || iters < 1) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
+  if (batch < 1 || batch > D->cfg.max_batch) return fail(c, CG_ERR_SHAPE, "decoder: batch out of range");
+  const int64_t M = batch;
+  CG_TRY(ensure_workspace(D, M));
+  cudaEvent_t e0, e1;
+  CG_CUDA(c, cudaEventCreate(&e0));
+  CG_CUDA(c, cudaEventCreate(&e1));
+  int st = CG_OK;
+  int64_t before = 0;
+  for (int it = -1; it < iters && st == CG_OK; ++it) {  // iteration -1 warms up
+    if (it == 0) { cudaEventRecord(e0, c->core->stream); before = c->launches; }
+    for (int li = 0; li < D->cfg.num_layers && st == CG_OK; ++li) {
+      Layer& L = D->layers[li];
+      st = gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0);
+      if (st == CG_OK) st = gemm(D, D->att, M, L.w_o, D->tmp->data(), nullptr, 0);
+      if (st == CG_OK) st = gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0);
+      if (st == CG_OK) st = gemm(D, D->hact, M, L.w_down, D->tmp->data(), nullptr, 0);
+    }
+    if (st == CG_OK) st = gemm(D, D->xl, M, D->head, D->logits->data(), nullptr, 0);
+  }
+  cudaEventRecord(e1, c->core->stream);
+  cudaEventSynchronize(e1);
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (st != CG_OK) return st;
+  *ms_per_sweep = ms / (float)iters;
+  if (launches_per_sweep) *launches_per_sweep = (int32_t)((c->launches - before) / iters);
+  return cg_sync(c);
+}
+
 int32_t cg_decoder_tokens(cg_decoder* D, cg_tensor** out) {
   if (!D || !out) return CG_ERR_INVALID;
   cg_ctx* c = D->c;

@@ -46,6 +46,7 @@ class Decoder:
             ("cg_decoder_step_with", [vp, vp, out]),
             ("cg_decoder_tokens", [vp, out]),
             ("cg_decoder_generate", [vp, vp, i32, i32, i32, vp]),
+            ("cg_decoder_time_gemms", [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i32)]),
         ]:
             fn = getattr(L, name)
             fn.argtypes = args
@@ -120,6 +121,12 @@ class Decoder:
         h = _c_vp()
         self.B._check(self.B._lib.cg_decoder_tokens(self._h, C.byref(h)))
         return self.B.to_numpy(self.B._wrap(h, U32))
+
+    def time_gemms(self, batch: int, iters: int = 20):
+        """(ms, launches) of the weight-streaming GEMMs of one decode step, measured on the device."""
+        ms, n = C.c_float(), C.c_int32()
+        self.B._check(self.B._lib.cg_decoder_time_gemms(self._h, int(batch), int(iters), C.byref(ms), C.byref(n)))
+        return ms.value, n.value
 
     def generate(self, prompt: np.ndarray, n_decode: int) -> np.ndarray:
         """Host buffers in, host buffers out: [B, S] ids -> [B, 1 + n_decode] greedy ids."""

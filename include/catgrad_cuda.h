@@ -265,6 +265,12 @@ int32_t cg_decoder_tokens(cg_decoder*, cg_tensor** out);
 int32_t cg_decoder_generate(cg_decoder*, const uint32_t* prompt, int32_t batch, int32_t seq,
                             int32_t n_decode, uint32_t* out);
 
+/* Measurement hook: enqueue only the weight-streaming GEMMs of one decode step for `batch`
+ * rows (every layer's qkv, o, gate/up, down projections and the LM head, on the decoder's
+ * own weights) `iters` times, timed with CUDA events on the context's stream. */
+int32_t cg_decoder_time_gemms(cg_decoder*, int32_t batch, int32_t iters, float* ms_per_sweep,
+                              int32_t* launches_per_sweep);
+
 /* --- tensor-parallel communicator (NCCL over NVLink; one process per GPU) --- */
 
 /* Size in bytes of the opaque id rank 0 creates and every rank must receive. */
