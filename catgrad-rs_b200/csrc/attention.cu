@@ -45,6 +45,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // ------------------------------------------------------------------ prefill ----------
 template <int D>
 __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int BQ = 64, BKV = 64, LD = D + 8;  // padded rows: conflict-free ldmatrix
   extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* sq = (__nv_bfloat16*)smem;
@@ -216,6 +218,8 @@ constexpr int MAX_REP = 8;      // query heads per kv head supported by the deco
 // scratch layout per (b, h, split): [m, l, o[0..d)]
 template <int D>
 __global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, int rep) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int E = D / 32;  // output elements per lane
   __shared__ float qs[MAX_REP][D];
   __shared__ float ps[4][MAX_REP][32];
@@ -257,7 +261,7 @@ __global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, in
     for (int r = 0; r < MAX_REP; ++r) sc[r] = 0.f;
     if (valid) {
       const uint4* krow = (const uint4*)(kbase + j * (int64_t)D);
-#pragma unroll 4
+#pragma unroll 8
       for (int ch = 0; ch < D / 8; ++ch) {
         const uint4 kv = krow[ch];
         const __nv_bfloat162* k2 = (const __nv_bfloat162*)&kv;
@@ -305,29 +309,34 @@ __global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, in
 #pragma unroll
         for (int e = 0; e < E; ++e) o[r][e] *= corr[r];
       }
-    const int nk = (int)std::min<int64_t>(32, t1 - c0);
-    for (int jj = 0; jj < nk; ++jj) {
-      const __nv_bfloat16* vrow = vbase + (c0 + jj) * (int64_t)D + lane * E;
-      float vf[E];
-      if (E == 2) {
-        const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)vrow);
-        vf[0] = f.x;
-        vf[1] = f.y;
-      } else {
+    // eight value rows per round, all loads issued before the first use; rows past the
+    // slice repeat its last row and carry probability 0
+    constexpr int VU = 8;
+#pragma unroll 1
+    for (int jj = 0; jj < 32; jj += VU) {
+      if (c0 + jj >= t1) break;
+      __nv_bfloat162 vraw[VU][E / 2];
 #pragma unroll
-        for (int e = 0; e < E; e += 2) {
-          const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)(vrow + e));
-          vf[e] = f.x;
-          vf[e + 1] = f.y;
-        }
+      for (int u = 0; u < VU; ++u) {
+        const int64_t row = std::min<int64_t>(c0 + jj + u, t1 - 1);
+        const __nv_bfloat162* vrow = (const __nv_bfloat162*)(vbase + row * (int64_t)D + lane * E);
+#pragma unroll
+        for (int e = 0; e < E / 2; ++e) vraw[u][e] = vrow[e];
       }
 #pragma unroll
-      for (int r = 0; r < MAX_REP; ++r)
-        if (r < rep) {
-          const float p = ps[warp][r][jj];
+      for (int u = 0; u < VU; ++u) {
 #pragma unroll
-          for (int e = 0; e < E; ++e) o[r][e] += p * vf[e];
-        }
+        for (int r = 0; r < MAX_REP; ++r)
+          if (r < rep) {
+            const float p = ps[warp][r][jj + u];
+#pragma unroll
+            for (int e = 0; e < E / 2; ++e) {
+              const float2 f = __bfloat1622float2(vraw[u][e]);
+              o[r][2 * e] += p * f.x;
+              o[r][2 * e + 1] += p * f.y;
+            }
+          }
+      }
     }
     __syncwarp();
   }
@@ -358,6 +367,8 @@ __global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, in
 
 template <int D>
 __global__ void k_attn_combine(const float* scratch, __nv_bfloat16* out, int nh) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int h = blockIdx.x;
   const int64_t b = blockIdx.y;
   const float* src = scratch + ((b * nh + h) * DEC_SPLITS) * (int64_t)(D + 2);
@@ -385,7 +396,7 @@ int launch_prefill(cg_ctx* c, const AttnArgs& a) {
   }
   dim3 grid((unsigned)((a.S + 63) / 64), (unsigned)a.nh, (unsigned)a.B);
   const float scale = 1.0f / sqrtf((float)D);
-  k_attn_prefill<D><<<grid, 128, smem, c->core->stream>>>(a, scale);
+  CG_CUDA(c, launch_kernel(c, k_attn_prefill<D>, grid, dim3(128), smem, 1, a, scale));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -395,10 +406,10 @@ int launch_decode(cg_ctx* c, const AttnArgs& a) {
   const int rep = a.nh / a.nkv;
   dim3 grid((unsigned)a.nkv, (unsigned)a.B, DEC_SPLITS);
   const float scale = 1.0f / sqrtf((float)D);
-  k_attn_decode<D><<<grid, 128, 0, c->core->stream>>>(a, scale, rep);
+  CG_CUDA(c, launch_kernel(c, k_attn_decode<D>, grid, dim3(128), 0, 1, a, scale, rep));
   CG_LAUNCHED(c);
   dim3 g2((unsigned)a.nh, (unsigned)a.B);
-  k_attn_combine<D><<<g2, D < 128 ? 64 : 128, 0, c->core->stream>>>(a.scratch, a.out, a.nh);
+  CG_CUDA(c, launch_kernel(c, k_attn_combine<D>, g2, dim3(D < 128 ? 64 : 128), 0, 1, (const float*)a.scratch, a.out, a.nh));
   CG_LAUNCHED(c);
   return CG_OK;
 }

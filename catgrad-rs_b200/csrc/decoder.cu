@@ -63,7 +63,7 @@ struct cg_decoder {
   // workspace (sized for `cap` tokens)
   int64_t cap = 0;
   cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *hact = nullptr,
-            *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *attn_scratch = nullptr;
+            *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *attn_scratch = nullptr, *best = nullptr;
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
   int64_t step_launches = 0;     // kernels in one decode step
@@ -237,7 +237,8 @@ int run_head(cg_decoder* D, int64_t B, int64_t S, bool advance) {
     if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllGather: ") + nccl().GetErrorString(r));
   }
   return k_launch_argmax(c, lg, B, D->Vp, cfg.tp_world, cfg.final_softcap, (uint32_t*)D->cur->data(),
-                         (uint32_t*)D->history->data(), cfg.max_seq, D->count_dev(), D->pos_dev(), advance ? 1 : 0);
+                         (uint32_t*)D->history->data(), cfg.max_seq, D->count_dev(), D->pos_dev(), advance ? 1 : 0,
+                         (unsigned long long*)D->best->data());
 }
 
 // One decode step for B rows reading position / count from device memory.
@@ -320,7 +321,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
-  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->attn_scratch);
+  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->attn_scratch); drop(D->best);
   delete D;
   return CG_OK;
 }
@@ -444,6 +445,9 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   n = std::max<int64_t>(32 * 64 * widest, (int64_t)300 * 128 * 256);
   CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->splitk));
   D->splitk_floats = n;
+  n = 2 * (int64_t)cfg.max_batch;  // one 64-bit argmax merge slot per row
+  CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->best));
+  CG_CUDA(c, cudaMemsetAsync(D->best->data(), 0, (size_t)n * 4, c->core->stream));
   n = attn_decode_scratch_floats(cfg.max_batch, D->nh, D->d);
   CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->attn_scratch));
   CG_TRY(ensure_workspace(D, cfg.max_batch));

@@ -51,6 +51,8 @@ __device__ __forceinline__ float gelu_f(float x) {
 
 __global__ void k_embed(const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,
                         int64_t vocab, int64_t H, float scale, float* out, int32_t* err) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t m = blockIdx.x;
   const int64_t b = m / S, sp = m - b * S;
   uint32_t t = tokens[b * tok_ld + tok_off + sp];
@@ -73,6 +75,8 @@ __global__ void k_embed(const uint32_t* tokens, int64_t tok_ld, int64_t tok_off,
 // One block per row.  MODE 0: out f32, 1: out bf16, 2: x_acc += normed(y)
 template <int MODE>
 __global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t H, void* out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float sh[32];
   const int64_t m = blockIdx.x;
   const float* row = x + m * ldx;
@@ -99,6 +103,8 @@ __global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float
 }
 
 __global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t m = blockIdx.y;
   const float* g = gu + m * 2 * F;
   const float* u = g + F;
@@ -170,6 +176,8 @@ __global__ void k_rope_apply(const float* x, const float* cos_t, const float* si
 // One warp per (token, head) of the fused qkv row: optional per-head RMSNorm, rotation,
 // bf16 store of q, append of k and v to the cache.
 __global__ void k_rope_store(RopeStoreArgs a) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int heads = a.nh + 2 * a.nkv;
   const int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -211,22 +219,28 @@ __global__ void k_rope_store(RopeStoreArgs a) {
 }
 
 // argmax over the vocabulary with the reference's ordering (total order on the bit patterns,
-// last index wins ties); optional soft-cap written back to the logits first.
-__global__ void k_argmax(float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
-                         uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance) {
+// last index wins ties), in two launches: every block folds a slice of one row into
+// (key << 32 | index) and merges it into best[row] with a 64-bit atomic max, which is
+// order-independent and therefore deterministic; a one-block kernel then publishes the
+// tokens.  An optional soft-cap is written back to the logits first.
+__global__ void k_argmax_part(float* logits, int64_t B, int64_t Vp, int parts, float softcap, unsigned long long* best_out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ unsigned long long sh[32];
-  const int64_t b = blockIdx.x;
+  const int64_t b = blockIdx.y;
+  const int64_t total = (int64_t)parts * Vp;
+  const int64_t span = (total + gridDim.x - 1) / gridDim.x;
+  const int64_t g0 = blockIdx.x * span, g1 = min(total, g0 + span);
   unsigned long long best = 0;
-  for (int part = 0; part < parts; ++part) {
-    float* row = logits + ((int64_t)part * B + b) * Vp;
-    for (int64_t i = threadIdx.x; i < Vp; i += blockDim.x) {
-      float v = row[i];
-      if (softcap > 0.f) { v = softcap * tanh_f(v / softcap); row[i] = v; }
-      uint32_t bits = __float_as_uint(v);
-      uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-      unsigned long long p = ((unsigned long long)key << 32) | (uint32_t)(part * Vp + i);
-      best = p > best ? p : best;
-    }
+  for (int64_t g = g0 + threadIdx.x; g < g1; g += blockDim.x) {
+    const int64_t part = g / Vp, i = g - part * Vp;
+    float* p = logits + (part * B + b) * Vp + i;
+    float v = *p;
+    if (softcap > 0.f) { v = softcap * tanh_f(v / softcap); *p = v; }
+    const uint32_t bits = __float_as_uint(v);
+    const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    const unsigned long long q = ((unsigned long long)key << 32) | (uint32_t)g;
+    best = q > best ? q : best;
   }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int o = 16; o; o >>= 1) {
@@ -241,20 +255,32 @@ __global__ void k_argmax(float* logits, int64_t B, int64_t Vp, int parts, float 
       unsigned long long w = __shfl_xor_sync(0xffffffffu, best, o);
       best = w > best ? w : best;
     }
-    if (lane == 0) {
-      const uint32_t t = (uint32_t)(best & 0xFFFFFFFFull);
-      tokens[b] = t;
-      if (history) history[b * hist_ld + *count_dev] = t;
-    }
+    if (lane == 0 && g0 < g1) atomicMax(best_out + b, best);
   }
 }
-// after every row has used the counters: one more generated token, one more cached position
-__global__ void k_advance(int64_t* count_dev, int64_t* pos_dev) {
-  *count_dev += 1;
-  *pos_dev += 1;
+// publish the tokens, clear the merge slots for the next step and, when asked, count one
+// more generated token and one more cached position
+__global__ void k_argmax_finish(unsigned long long* best, int64_t B, uint32_t* tokens, uint32_t* history, int64_t hist_ld,
+                                int64_t* count_dev, int64_t* pos_dev, int advance) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t count = *count_dev;
+  for (int64_t b = threadIdx.x; b < B; b += blockDim.x) {
+    const uint32_t t = (uint32_t)(best[b] & 0xFFFFFFFFull);
+    tokens[b] = t;
+    if (history) history[b * hist_ld + count] = t;
+    best[b] = 0ull;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && advance) {
+    *count_dev = count + 1;
+    *pos_dev += 1;
+  }
 }
 
 __global__ void k_to_bf16(const float* x, int64_t n, __nv_bfloat16* out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16_rn(x[i]);
 }
@@ -264,8 +290,8 @@ __global__ void k_to_bf16(const float* x, int64_t n, __nv_bfloat16* out) {
 int k_launch_embed(cg_ctx* c, const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,
                    int64_t vocab, int64_t M, int64_t H, float scale, float* out) {
   if (M == 0) return CG_OK;
-  k_embed<<<(unsigned)M, 256, 0, c->core->stream>>>(tokens, tok_ld, tok_off, S, table, st, vocab, H, scale, out,
-                                                   c->core->dev_err);
+  CG_CUDA(c, launch_kernel(c, k_embed, dim3((unsigned)M), dim3(256), 0, 1, tokens, tok_ld, tok_off, S, table, st, vocab, H,
+                           scale, out, c->core->dev_err));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -274,8 +300,8 @@ int k_launch_rmsnorm(cg_ctx* c, const float* x, int64_t ldx, const float* gamma,
                      int64_t H, void* out, int out_bf16) {
   if (M == 0) return CG_OK;
   const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  if (out_bf16) k_rmsnorm<1><<<(unsigned)M, block, 0, c->core->stream>>>(x, ldx, gamma, eps, plus_one, H, out);
-  else k_rmsnorm<0><<<(unsigned)M, block, 0, c->core->stream>>>(x, ldx, gamma, eps, plus_one, H, out);
+  if (out_bf16) CG_CUDA(c, launch_kernel(c, k_rmsnorm<1>, dim3((unsigned)M), dim3(block), 0, 1, x, ldx, gamma, eps, plus_one, H, out));
+  else CG_CUDA(c, launch_kernel(c, k_rmsnorm<0>, dim3((unsigned)M), dim3(block), 0, 1, x, ldx, gamma, eps, plus_one, H, out));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -284,7 +310,7 @@ int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float ep
                          float* x) {
   if (M == 0) return CG_OK;
   const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  k_rmsnorm<2><<<(unsigned)M, block, 0, c->core->stream>>>(y, H, gamma, eps, plus_one, H, x);
+  CG_CUDA(c, launch_kernel(c, k_rmsnorm<2>, dim3((unsigned)M), dim3(block), 0, 1, y, H, gamma, eps, plus_one, H, (void*)x));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -292,7 +318,7 @@ int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float ep
 int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out) {
   if (M == 0 || F == 0) return CG_OK;
   dim3 grid((unsigned)std::min<int64_t>((F + 255) / 256, 64), (unsigned)M);
-  k_act_mul<<<grid, 256, 0, c->core->stream>>>(gu, F, act, out);
+  CG_CUDA(c, launch_kernel(c, k_act_mul, grid, dim3(256), 0, 1, gu, F, act, out));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -311,27 +337,28 @@ int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
   if (warps == 0) return CG_OK;
   const int block = 256;
   const int64_t blocks = (warps * 32 + block - 1) / block;
-  k_rope_store<<<(unsigned)blocks, block, 0, c->core->stream>>>(a);
+  CG_CUDA(c, launch_kernel(c, k_rope_store, dim3((unsigned)blocks), dim3(block), 0, 1, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }
 
 int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
-                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance) {
+                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
+                    unsigned long long* best) {
   if (B == 0) return CG_OK;
-  k_argmax<<<(unsigned)B, 1024, 0, c->core->stream>>>(logits, B, Vp, parts, softcap, tokens, history, hist_ld, count_dev,
-                                                     pos_dev, advance);
+  const int64_t total = (int64_t)parts * Vp;
+  const unsigned chunks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(64, total / 1024));
+  CG_CUDA(c, launch_kernel(c, k_argmax_part, dim3(chunks, (unsigned)B), dim3(256), 0, 1, logits, B, Vp, parts, softcap, best));
   CG_LAUNCHED(c);
-  if (advance) {
-    k_advance<<<1, 1, 0, c->core->stream>>>(count_dev, pos_dev);
-    CG_LAUNCHED(c);
-  }
+  CG_CUDA(c, launch_kernel(c, k_argmax_finish, dim3(1), dim3(64), 0, 1, best, B, tokens, history, hist_ld, count_dev, pos_dev,
+                           advance));
+  CG_LAUNCHED(c);
   return CG_OK;
 }
 
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out) {
   if (n == 0) return CG_OK;
-  k_to_bf16<<<grid_for(n, 256), 256, 0, c->core->stream>>>(x, n, out);
+  CG_CUDA(c, launch_kernel(c, k_to_bf16, dim3(grid_for(n, 256)), dim3(256), 0, 1, x, n, out));
   CG_LAUNCHED(c);
   return CG_OK;
 }

@@ -7,16 +7,29 @@
 // kernel serves decode (TN = 16, HBM-bound weight streaming with split-K) and prefill
 // (TN = 256, tensor-bound).
 //
-// Pipeline per CTA (192 threads, 1 CTA per SM):
+// Pipeline per CTA (192 threads):
 //   warp 0      one lane issues TMA loads (128B-swizzled [rows, 64] bf16 boxes) into a
 //               ring of STAGES shared-memory slots, signalled through mbarriers
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma (128 x TN x 16, f32 accumulate
 //               in TMEM) and commits slot releases / the final "accumulator ready"
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (lane = output feature, column =
 //               token) and store coalesced along the feature axis
+//
+// Weights never depend on the kernel that ran before, so under programmatic dependent
+// launch the producer fills the ring with weight tiles BEFORE it waits for the preceding
+// kernel; only activation tiles, the residual and the stores come after the wait.  HBM keeps
+// streaming while the small kernels between two GEMMs run.
+//
+// Split-K: the `splits` CTAs that share an output tile form a thread-block cluster; each
+// leaves its partial tile in its own shared memory and, after a cluster barrier, CTA r sums
+// rows [r * 128 / splits, ...) of all partials over distributed shared memory in rank
+// order (deterministic) and stores them.  No partials in HBM, no second kernel.
+//
 // Every mbarrier wait is bounded (about one second); on expiry the kernel raises the
-// context's error word, still frees its TMEM and returns.
+// context's error word, still passes its cluster barriers, frees its TMEM and returns.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "runtime.h"
 
@@ -32,11 +45,12 @@ constexpr uint32_t A_BYTES = BM * BK * 2;
 struct TcArgs {
   void* out;
   const float* residual;
-  float* partial;
+  float* partial;  // only when splits > 1 without a cluster
   int64_t ldo;
   int M, N, K;
   int out_mode;  // 0 f32, 1 bf16, 2 f32 + residual
   int kb_total, kb_per_split, splits;
+  int cluster;   // 1: the splits of a tile are one cluster and reduce over shared memory
   int32_t* err;
 };
 
@@ -122,13 +136,33 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 
-template <int TN, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__device__ __forceinline__ void store_out(const TcArgs& p, int m, int n, float acc) {
+  const int64_t o = (int64_t)m * p.ldo + n;
+  if (p.out_mode == 0) ((float*)p.out)[o] = acc;
+  else if (p.out_mode == 1) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(acc);
+  else ((float*)p.out)[o] = acc + p.residual[o];
+}
+
+template <int TN, int STAGES, int MINB>
+__global__ void __launch_bounds__(192, MINB)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs p) {
   constexpr uint32_t B_BYTES = TN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t NCOLS = TN < 32 ? 32 : TN;  // TMEM columns: power of two >= 32
+
+  // the next kernel in the stream may start its own prologue now
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -147,7 +181,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bars + 8 * s, 1);             // full[s]: producer's expect_tx arrival + bytes
+      mbar_init(bars + 8 * s, 2);             // full[s]: weight arrival + activation arrival
       mbar_init(bars + 8 * (STAGES + s), 1);  // empty[s]: one tcgen05.commit
     }
     mbar_init(bar_accum, 1);
@@ -166,17 +200,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = *tmem_slot;
 
+  bool acc_ok = false;  // epilogue warps: the accumulator is complete
   if (warp == 0) {
     if (lane == 0 && nkb > 0) {
+      // weights first: they do not depend on the preceding kernel
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t full = bars + 8 * i;
+        mbar_expect_tx(full, A_BYTES);
+        tma_load_2d(base + i * STAGE_BYTES, &map_w, (kb0 + i) * BK, n0, full);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
-        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-        if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
         const uint32_t full = bars + 8 * s;
-        mbar_expect_tx(full, STAGE_BYTES);
         const uint32_t a = base + s * STAGE_BYTES;
         const int k = (kb0 + i) * BK;
-        tma_load_2d(a, &map_w, k, n0, full);
+        if (i >= pre) {
+          const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+          if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
+          mbar_expect_tx(full, A_BYTES);
+          tma_load_2d(a, &map_w, k, n0, full);
+        }
+        mbar_expect_tx(full, B_BYTES);
         tma_load_2d(a + A_BYTES, &map_x, k, m0, full);
       }
     }
@@ -201,38 +247,63 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       }
       if (ok) umma_commit(bar_accum);
     }
-  } else if (nkb > 0) {
+  } else {
+    // outputs (and the residual) belong to the stream order: wait for the preceding kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (nkb > 0) {
+      acc_ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+  }
+
+  if (warp >= 2 && acc_ok) {
     // TMEM lanes a warp may read: 32 * (warp id mod 4)
     const int q = warp & 3;
-    const int n = n0 + q * 32 + lane;
-    const bool ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    const int row = q * 32 + lane;
+    const int n = n0 + row;
+    float* stage = (float*)gen;  // [TN][128] partial tile; the ring is idle by now
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 16) {
-        if (m0 + c0 >= p.M) break;
-        uint32_t v[16];
-        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (n < p.N) {
+    for (int c0 = 0; c0 < TN; c0 += 16) {
+      if (m0 + c0 >= p.M) break;
+      uint32_t v[16];
+      tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (p.cluster) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m >= p.M) break;
-            const float acc = __uint_as_float(v[j]);
-            if (p.splits > 1) {
-              p.partial[((int64_t)split * p.M + m) * p.N + n] = acc;
-            } else if (p.out_mode == 0) {
-              ((float*)p.out)[(int64_t)m * p.ldo + n] = acc;
-            } else if (p.out_mode == 1) {
-              ((__nv_bfloat16*)p.out)[(int64_t)m * p.ldo + n] = __float2bfloat16_rn(acc);
-            } else {
-              ((float*)p.out)[(int64_t)m * p.ldo + n] = acc + p.residual[(int64_t)m * p.ldo + n];
-            }
-          }
+        for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = __uint_as_float(v[j]);
+      } else if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c0 + j;
+          if (m >= p.M) break;
+          const float acc = __uint_as_float(v[j]);
+          if (p.splits > 1) p.partial[((int64_t)split * p.M + m) * p.N + n] = acc;
+          else store_out(p, m, n, acc);
         }
       }
     }
+  }
+
+  if (p.cluster) {
+    // all partial tiles of this output tile are in their CTAs' shared memory
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && !*cta_abort) {
+      const int S = p.splits;
+      const int rows_per = BM / S;
+      const int cols = min(TN, p.M - m0);
+      const uint32_t stage_u = base;
+      for (int e = tid - 64; e < rows_per * cols; e += 128) {
+        const int col = e / rows_per;
+        const int row = split * rows_per + (e - col * rows_per);
+        float acc = 0.f;
+        for (int s = 0; s < S; ++s) acc += ld_cluster_f32(stage_u + (uint32_t)(col * BM + row) * 4u, (uint32_t)s);
+        const int n = n0 + row;
+        if (n < p.N) store_out(p, m0 + col, n, acc);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -243,9 +314,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   }
 }
 
-// out = sum over splits of partial (+ residual), in the output precision.
+// out = sum over splits of partial (+ residual), in the output precision (only used when the
+// splits of a tile could not form a cluster).
 __global__ void k_splitk_reduce(const float* partial, int splits, int64_t M, int64_t N, void* out, int64_t ldo,
                                 const float* residual, int out_mode) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t total = M * N;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
@@ -283,15 +357,15 @@ int make_map(cg_ctx* c, CUtensorMap* map, const void* ptr, int64_t rows, int64_t
   return CG_OK;
 }
 
-template <int TN, int STAGES>
+template <int TN, int STAGES, int MINB>
 int launch(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES + TN * BK * 2) + 1024 + 16 * STAGES + 64;
   static bool configured = false;  // per instantiation; the attribute is per function and device-wide
   if (!configured) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  k_gemm_tc<TN, STAGES><<<grid, 192, smem, c->core->stream>>>(mw, mx, a);
+  CG_CUDA(c, launch_kernel(c, k_gemm_tc<TN, STAGES, MINB>, grid, dim3(192), smem, a.cluster ? a.splits : 1, mw, mx, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -305,10 +379,10 @@ int gemm_tc_pick_splits(int64_t M, int64_t N, int64_t K) {
   const int64_t tiles = ((N + BM - 1) / BM) * ((M + tn - 1) / tn);
   const int64_t kb = (K + BK - 1) / BK;
   if (tiles >= 148 || kb < 8) return 1;
-  int64_t s = (2 * 148 + tiles - 1) / tiles;
-  s = std::min<int64_t>(s, kb / 4);
-  s = std::min<int64_t>(s, 32);
-  return (int)std::max<int64_t>(s, 1);
+  // a power of two up to 8 (one portable cluster), at least two k blocks per slice
+  int s = 1;
+  while (s < 8 && tiles * (s * 2) <= 2 * 148 + 32 && kb / (s * 2) >= 2) s *= 2;
+  return s;
 }
 
 int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, void* out, int64_t ldo,
@@ -323,9 +397,11 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
   splits = std::min(splits, kb_total);
   int kb_per = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per - 1) / kb_per;  // no empty slices
+  // a cluster needs a power-of-two size up to 8 and a tile that fits the staging area
+  const bool cluster = splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && tn <= 64;
 
   Hold ws;
-  if (splits > 1 && !workspace) {
+  if (splits > 1 && !cluster && !workspace) {
     int64_t n = (int64_t)splits * M * N;
     CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &ws.t));
     workspace = (float*)ws.t->data();
@@ -347,19 +423,20 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
   a.kb_total = kb_total;
   a.kb_per_split = kb_per;
   a.splits = splits;
+  a.cluster = cluster ? 1 : 0;
   a.err = c->core->dev_err;
   dim3 grid((unsigned)((N + BM - 1) / BM), (unsigned)((M + tn - 1) / tn), (unsigned)splits);
   if (grid.y > 65535) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: too many token tiles");
   switch (tn) {
-    case 16: CG_TRY((launch<16, 10>(c, mw, mx, a, grid))); break;
-    case 32: CG_TRY((launch<32, 10>(c, mw, mx, a, grid))); break;
-    case 64: CG_TRY((launch<64, 8>(c, mw, mx, a, grid))); break;
-    case 128: CG_TRY((launch<128, 6>(c, mw, mx, a, grid))); break;
-    default: CG_TRY((launch<256, 4>(c, mw, mx, a, grid))); break;
+    case 16: CG_TRY((launch<16, 6, 2>(c, mw, mx, a, grid))); break;
+    case 32: CG_TRY((launch<32, 5, 2>(c, mw, mx, a, grid))); break;
+    case 64: CG_TRY((launch<64, 4, 2>(c, mw, mx, a, grid))); break;
+    case 128: CG_TRY((launch<128, 6, 1>(c, mw, mx, a, grid))); break;
+    default: CG_TRY((launch<256, 4, 1>(c, mw, mx, a, grid))); break;
   }
-  if (splits > 1) {
-    k_splitk_reduce<<<grid_for(M * N, 256), 256, 0, c->core->stream>>>(workspace, splits, M, N, out, ldo, residual,
-                                                                     out_mode);
+  if (splits > 1 && !cluster) {
+    CG_CUDA(c, launch_kernel(c, k_splitk_reduce, dim3(grid_for(M * N, 256)), dim3(256), 0, 1, (const float*)workspace, splits,
+                             M, N, out, ldo, residual, out_mode));
     CG_LAUNCHED(c);
   }
   return CG_OK;

@@ -69,9 +69,11 @@ int64_t attn_decode_scratch_floats(int64_t B, int nh, int d);
 // soft-cap applied to the logits in place first.  The logits are `parts` vocabulary slices of
 // Vp entries laid out [parts, B, Vp] (parts = 1: plain [B, V]).  Also appends the token to
 // history[b * hist_ld + n] where n = *count_dev (a device counter) and, if advance != 0,
-// increments *count_dev and *pos_dev afterwards.
+// increments *count_dev and *pos_dev afterwards.  `best` is B zeroed 64-bit merge slots;
+// they are zero again when the call has run.
 int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, float softcap, uint32_t* tokens,
-                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance);
+                    uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
+                    unsigned long long* best);
 
 // f32 -> bf16 rows (ld in elements for the source)
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out);

@@ -61,6 +61,7 @@ struct cg_ctx {
   std::string err;
   int64_t launches = 0;
   int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
+  int opt_pdl = 1;        // programmatic dependent launch for the fused kernels
   void* comm = nullptr;   // ncclComm_t
   int comm_rank = 0, comm_world = 1;
   // host function pointer of cuTensorMapEncodeTiled, resolved on first use
@@ -151,6 +152,37 @@ struct Iter {
 // Build an Iter from shapes/strides, merging adjacent dims that are jointly contiguous
 // in every operand and dropping unit dims.  Unused operands pass nullptr strides.
 Iter make_iter(int rank, const int64_t* dims, const int64_t* s0, const int64_t* s1, const int64_t* s2);
+
+// Launch on the context's stream with programmatic dependent launch (the kernel may start
+// before its predecessor in the stream has finished; it must execute griddepcontrol.wait
+// before it reads or writes anything the predecessor touches) and, when cluster_z > 1, as
+// thread-block clusters of (1, 1, cluster_z).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(cg_ctx* c, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_z,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = c->core->stream;
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (c->opt_pdl) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = (unsigned)cluster_z;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 inline int grid_for(int64_t n, int block, int max_blocks = 148 * 16) {
   int64_t g = (n + block - 1) / block;
