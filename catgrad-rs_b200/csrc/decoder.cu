@@ -133,10 +133,26 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   return CG_OK;
 }
 
-// y = x W^T (+ residual) with every rank's partial summed when the weight is row-split.
-// mode: 0 -> f32 out, 2 -> out = residual + product (residual may alias out).
-int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, void* out, const float* residual, int mode) {
-  const int64_t N = w->dims[0], K = w->dims[1];
+// y = x W^T (+ residual) on bf16 activations.  mode: 0 -> f32 out, 1 -> bf16 out,
+// 2 -> out = residual + product (residual may alias out).  A handful of tokens takes the
+// weight-streaming kernel (optionally with the fused gate/up epilogue), larger token counts
+// the tiled kernel.
+bool small_m(int64_t M, int64_t K) { return gemm_dec_supported(M, K); }
+
+int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, void* out, const float* residual, int mode,
+         bool dual = false) {
+  const int64_t K = w->dims[1];
+  const int64_t N = dual ? w->dims[0] / 2 : w->dims[0];
+  if (small_m(M, K)) {
+    DecGemm g;
+    g.x = (const __nv_bfloat16*)xin->data(); g.ldx = K;
+    g.w = (const __nv_bfloat16*)w->data(); g.ldw = K; g.w_rows = w->dims[0];
+    g.out = out; g.ldo = N; g.residual = residual; g.out_mode = mode;
+    g.dual = dual ? 1 : 0; g.act = D->cfg.act;
+    g.M = M; g.N = N; g.K = K;
+    return gemm_dec(D->c, g);
+  }
+  if (dual) return fail(D->c, CG_ERR_INVALID, "decoder: the fused gate/up epilogue is a decode-path feature");
   const int splits = gemm_tc_pick_splits(M, N, K);
   float* ws = (int64_t)splits * M * N <= D->splitk_floats ? (float*)D->splitk->data() : nullptr;
   return gemm_tc(D->c, (const __nv_bfloat16*)xin->data(), K, (const __nv_bfloat16*)w->data(), K, out, N, residual, M, N, K,
@@ -179,6 +195,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
   const int64_t M = B * S;
   for (int li = 0; li < cfg.num_layers; ++li) {
     Layer& L = D->layers[li];
+    const bool small = small_m(M, D->H);
     CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                             cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0));
@@ -212,11 +229,15 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     if (S == 1) CG_TRY(k_launch_attn_decode(c, a));
     else CG_TRY(k_launch_attn_prefill(c, a));
     CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn));
-    const cg_tensor* ln2 = L.ln_pre_ffn;
-    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)ln2->data(), cfg.rms_eps, cfg.norm_plus_one,
-                            M, D->H, D->xn->data(), 1));
-    CG_TRY(gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0));
-    CG_TRY(k_launch_act_mul(c, (const float*)D->gu->data(), M, D->F, cfg.act, (__nv_bfloat16*)D->hact->data()));
+    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
+                            cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    if (small) {
+      // gate/up projections and act(gate) * up in one kernel
+      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
+    } else {
+      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0));
+      CG_TRY(k_launch_act_mul(c, (const float*)D->gu->data(), M, D->F, cfg.act, (__nv_bfloat16*)D->hact->data()));
+    }
     CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn));
   }
   return CG_OK;
@@ -565,11 +586,13 @@ int32_t cg_decoder_time_gemms(cg_decoder* D, int32_t batch, int32_t iters, float
   int64_t before = 0;
   for (int it = -1; it < iters && st == CG_OK; ++it) {  // iteration -1 warms up
     if (it == 0) { cudaEventRecord(e0, c->core->stream); before = c->launches; }
+    const bool small = small_m(M, D->H);
     for (int li = 0; li < D->cfg.num_layers && st == CG_OK; ++li) {
       Layer& L = D->layers[li];
       st = gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0);
       if (st == CG_OK) st = gemm(D, D->att, M, L.w_o, D->tmp->data(), nullptr, 0);
-      if (st == CG_OK) st = gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0);
+      if (st == CG_OK) st = small ? gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 1, true)
+                                  : gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0);
       if (st == CG_OK) st = gemm(D, D->hact, M, L.w_down, D->tmp->data(), nullptr, 0);
     }
     if (st == CG_OK) st = gemm(D, D->xl, M, D->head, D->logits->data(), nullptr, 0);

@@ -2,6 +2,7 @@
 // spreads over a chain of primitive backend calls with materialised intermediates
 // (catgrad/src/stdlib/nn/mod.rs:117-171, catgrad-llm/src/helpers.rs:120-271).
 // Rows are reduced with warp shuffles; loads are 128-bit where the row length allows.
+#include "act.cuh"
 #include "kernels.h"
 
 #include <algorithm>
@@ -38,15 +39,6 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
   __syncthreads();
   v = lane < nw ? sh[lane] : -INFINITY;
   return warp_max(v);
-}
-
-// sigmoid / tanh / silu / gelu spelled as the stdlib composes them (nn/mod.rs:130-160)
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
-__device__ __forceinline__ float tanh_f(float x) { return 2.f * sigmoid_f(2.f * x) - 1.f; }
-__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
-__device__ __forceinline__ float gelu_f(float x) {
-  const float c = 0.7978845608f;  // sqrt(2/pi) in f32
-  return 0.5f * x * (1.f + tanh_f(c * (x + 0.044715f * x * x * x)));
 }
 
 __global__ void k_embed(const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,

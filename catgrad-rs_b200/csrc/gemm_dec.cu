@@ -1,0 +1,320 @@
+// gemm_dec.cu — the decode-step GEMM: y[M, N] = x[M, K] w[N, K]^T for M <= 32 tokens.
+//
+// With a handful of tokens the linear layers of catgrad-llm/src/models/llama.rs:12-115 are
+// pure weight streaming, so this kernel is built around keeping HBM busy:
+//
+//   * warp 0 streams 128-row weight tiles by TMA into a shared-memory ring and starts doing
+//     so BEFORE the preceding kernel has finished (programmatic dependent launch): weights
+//     do not depend on it.  Only the small bf16 activation tiles wait for the predecessor.
+//   * a CTA keeps its shared-memory ring small (about a third of an SM) so that the CTAs of
+//     the NEXT GEMM in the stream can already be resident and prefetching their weights while
+//     this one computes: the HBM stream does not stop at kernel boundaries.
+//   * warp 1 issues tcgen05.mma (128 x TN x 16, f32 accumulators in TMEM).  For the gate/up
+//     pair of the FFN both 128-row tiles share the CTA and the epilogue writes
+//     act(gate) * up directly (llama.rs:27), so the [M, 2F] intermediate never exists.
+//   * split-K partials are summed in rank order over distributed shared memory inside a
+//     thread-block cluster (deterministic), then the epilogue (residual add / bf16 / act)
+//     is applied once.
+//
+// All waits are bounded; on expiry the context's error word is raised and the kernel still
+// passes its cluster barriers, frees its TMEM and returns.
+#include <algorithm>
+
+#include "act.cuh"
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace cg {
+
+namespace {
+
+using namespace tc;
+
+struct DecArgs {
+  void* out;
+  int64_t ldo;
+  const float* residual;
+  int out_mode;
+  int dual, act, up_off;
+  int M, N, K;
+  int kb_total, kb_per_split, splits, stages;
+  int32_t* err;
+  int trace;  // slot in the timeline buffer, or -1
+};
+
+// Timeline of the decode GEMM launches (diagnostics): per slot {first CTA start, predecessor
+// complete, last accumulator ready, last CTA end} in globaltimer nanoseconds.
+constexpr int TRACE_SLOTS = 2048;
+__device__ unsigned long long g_trace[TRACE_SLOTS * 4];
+
+__device__ __forceinline__ void trace_min(int slot, int f) {
+  if (slot >= 0) atomicMin(&g_trace[slot * 4 + f], (unsigned long long)globaltimer());
+}
+__device__ __forceinline__ void trace_max(int slot, int f) {
+  if (slot >= 0) atomicMax(&g_trace[slot * 4 + f], (unsigned long long)globaltimer());
+}
+
+__device__ __forceinline__ void finish(const DecArgs& p, int m, int n, float g, float u) {
+  float v = g;
+  if (p.dual) v = (p.act == 0 ? silu_f(g) : gelu_f(g)) * u;
+  const int64_t o = (int64_t)m * p.ldo + n;
+  if (p.out_mode == 0) ((float*)p.out)[o] = v;
+  else if (p.out_mode == 1) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+  else ((float*)p.out)[o] = v + p.residual[o];
+}
+
+template <int TN>
+__global__ void __launch_bounds__(192, 3)
+k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, DecArgs p) {
+  constexpr uint32_t X_TILE = TN * BK * 2;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const int STAGES = p.stages;
+  const uint32_t wbytes = p.dual ? 2 * A_BYTES : A_BYTES;
+  const uint32_t stage_bytes = wbytes + X_TILE;
+  const uint32_t boff = STAGES * stage_bytes;
+  const uint32_t bars = base + boff;  // full[STAGES], empty[STAGES], accum
+  const uint32_t bar_accum = bars + 16 * STAGES;
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen + boff + 16 * STAGES + 8);
+  volatile int* cta_abort = (volatile int*)(gen + boff + 16 * STAGES + 12);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * BM, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_total, kb0 + p.kb_per_split) - kb0;
+  const uint32_t ncols = p.dual ? 2 * TN : (TN < 32 ? 32 : TN);
+  if (tid == 0) trace_min(p.trace, 0);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bars + 8 * s, 2);             // full[s]: weight arrival + activation arrival
+      mbar_init(bars + 8 * (STAGES + s), 1);  // empty[s]: one tcgen05.commit
+    }
+    mbar_init(bar_accum, 1);
+    *cta_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  bool acc_ok = false;
+  if (warp == 0) {
+    if (lane == 0 && nkb > 0) {
+      // weights first: they do not depend on the preceding kernel
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t full = bars + 8 * i;
+        const uint32_t a = base + i * stage_bytes;
+        const int k = (kb0 + i) * BK;
+        mbar_expect_tx(full, wbytes);
+        tma_load_2d(a, &map_w, k, n0, full);
+        if (p.dual) tma_load_2d(a + A_BYTES, &map_w, k, p.up_off + n0, full);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      trace_min(p.trace, 1);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t full = bars + 8 * s;
+        const uint32_t a = base + s * stage_bytes;
+        const int k = (kb0 + i) * BK;
+        if (i >= pre) {
+          const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+          if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
+          mbar_expect_tx(full, wbytes);
+          tma_load_2d(a, &map_w, k, n0, full);
+          if (p.dual) tma_load_2d(a + A_BYTES, &map_w, k, p.up_off + n0, full);
+        }
+        mbar_expect_tx(full, X_TILE);
+        tma_load_2d(a + wbytes, &map_x, k, 0, full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkb > 0) {
+      const uint32_t idesc = umma_idesc(TN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(bars + 8 * s, ph, cta_abort, p.err);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = base + s * stage_bytes;
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          const uint64_t db = umma_desc(a + wbytes + kk * UMMA_K * 2);
+          umma_bf16(tmem_acc, umma_desc(a + kk * UMMA_K * 2), db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          if (p.dual) umma_bf16(tmem_acc + TN, umma_desc(a + A_BYTES + kk * UMMA_K * 2), db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(bars + 8 * (STAGES + s));
+      }
+      if (ok) umma_commit(bar_accum);
+    }
+  } else {
+    // outputs (and the residual) belong to the stream order: wait for the preceding kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (nkb > 0) {
+      acc_ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (tid == 64) trace_max(p.trace, 2);
+    }
+  }
+
+  const bool cluster = p.splits > 1;
+  if (warp >= 2 && acc_ok) {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int n = n0 + row;
+    float* stage = (float*)gen;  // [2][TN][128] partial tiles; the ring is idle by now
+#pragma unroll 1
+    for (int c0 = 0; c0 < TN; c0 += 16) {
+      if (c0 >= p.M) break;
+      uint32_t g[16], u[16];
+      tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, g);
+      if (p.dual) tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(TN + c0), u);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (cluster) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          stage[(c0 + j) * BM + row] = __uint_as_float(g[j]);
+          if (p.dual) stage[(TN + c0 + j) * BM + row] = __uint_as_float(u[j]);
+        }
+      } else if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j >= p.M) break;
+          finish(p, c0 + j, n, __uint_as_float(g[j]), p.dual ? __uint_as_float(u[j]) : 0.f);
+        }
+      }
+    }
+  }
+
+  if (cluster) {
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && !*cta_abort) {
+      const int S = p.splits;
+      const int rows_per = BM / S;
+      const int cols = min(TN, p.M);
+      for (int e = tid - 64; e < rows_per * cols; e += 128) {
+        const int col = e / rows_per;
+        const int row = split * rows_per + (e - col * rows_per);
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < S; ++s) {
+          g += ld_cluster_f32(base + (uint32_t)(col * BM + row) * 4u, (uint32_t)s);
+          if (p.dual) u += ld_cluster_f32(base + (uint32_t)((TN + col) * BM + row) * 4u, (uint32_t)s);
+        }
+        const int n = n0 + row;
+        if (n < p.N) finish(p, col, n, g, u);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
+  }
+  if (tid == 0) trace_max(p.trace, 3);
+}
+
+template <int TN>
+int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const DecArgs& a, dim3 grid, size_t smem) {
+  static size_t configured = 0;  // largest dynamic shared memory size set so far
+  if (smem > configured) {
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  CG_CUDA(c, launch_kernel(c, k_gemm_dec<TN>, grid, dim3(192), smem, a.splits, mw, mx, a));
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+}  // namespace
+
+bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 8 == 0; }
+
+int gemm_dec(cg_ctx* c, const DecGemm& g) {
+  if (g.M <= 0 || g.N <= 0) return CG_OK;
+  if (!gemm_dec_supported(g.M, g.K) || g.K <= 0 || g.ldw % 8 || g.ldx % 8 || ((uintptr_t)g.w % 16) || ((uintptr_t)g.x % 16))
+    return fail(c, CG_ERR_UNSUPPORTED, "gemm_dec: unsupported shape or alignment");
+  const int tn = g.M <= 16 ? 16 : 32;
+  const int64_t tiles = (g.N + BM - 1) / BM;
+  const int kb_total = (int)((g.K + BK - 1) / BK);
+  // split-K: a power of two up to 8 (one portable cluster), about two CTAs per SM in total,
+  // at least two k blocks per CTA
+  int splits = 1;
+  while (splits < 8 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
+  int kb_per = (kb_total + splits - 1) / splits;
+  if ((kb_total + kb_per - 1) / kb_per != splits) {  // an empty slice would break the cluster shape
+    splits = 1;
+    kb_per = kb_total;
+  }
+  const size_t wbytes = g.dual ? 2 * A_BYTES : A_BYTES;
+  const size_t stage = wbytes + (size_t)tn * BK * 2;
+  // about a third of an SM's shared memory per CTA, so the next GEMM's CTAs can be resident
+  // (and prefetching their weights) while this one computes
+  const size_t budget = 72 * 1024;
+  int stages = (int)std::max<size_t>(2, budget / stage);
+  stages = std::min(stages, std::max(kb_per, 2));
+  stages = std::min(stages, 8);
+  const size_t stage_need = (size_t)(g.dual ? 2 : 1) * tn * BM * 4;  // cluster-reduce staging lives in the ring
+  while (splits > 1 && stage_need > (size_t)stages * stage) ++stages;
+  const size_t smem = (size_t)stages * stage + 1024 + 16 * 8 + 64;
+
+  CUtensorMap mw, mx;
+  CG_TRY(make_map(c, &mw, g.w, g.w_rows, g.K, g.ldw, BM));
+  CG_TRY(make_map(c, &mx, g.x, g.M, g.K, g.ldx, tn));
+  DecArgs a;
+  a.out = g.out; a.ldo = g.ldo; a.residual = g.residual; a.out_mode = g.out_mode;
+  a.dual = g.dual; a.act = g.act; a.up_off = (int)g.N;
+  a.M = (int)g.M; a.N = (int)g.N; a.K = (int)g.K;
+  a.kb_total = kb_total; a.kb_per_split = kb_per; a.splits = splits; a.stages = stages;
+  a.err = c->core->dev_err;
+  a.trace = c->trace_on ? (int)(c->trace_next++ % TRACE_SLOTS) : -1;
+  dim3 grid((unsigned)tiles, 1, (unsigned)splits);
+  if (tn == 16) return launch_dec<16>(c, mw, mx, a, grid, smem);
+  return launch_dec<32>(c, mw, mx, a, grid, smem);
+}
+
+}  // namespace cg
+
+using namespace cg;
+
+extern "C" int32_t cg_trace_enable(cg_ctx* c, int32_t on) {
+  if (!c) return CG_ERR_INVALID;
+  c->trace_on = on != 0;
+  c->trace_next = 0;
+  if (on) {
+    std::vector<unsigned long long> init((size_t)TRACE_SLOTS * 4);
+    for (int i = 0; i < TRACE_SLOTS; ++i) {
+      init[i * 4 + 0] = init[i * 4 + 1] = ~0ull;
+      init[i * 4 + 2] = init[i * 4 + 3] = 0ull;
+    }
+    CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
+    CG_CUDA(c, cudaMemcpyToSymbol(g_trace, init.data(), init.size() * 8));
+  }
+  return CG_OK;
+}
+
+extern "C" int32_t cg_trace_read(cg_ctx* c, uint64_t* out, int32_t slots) {
+  if (!c || !out || slots < 0 || slots > TRACE_SLOTS) return CG_ERR_INVALID;
+  CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
+  CG_CUDA(c, cudaMemcpyFromSymbol(out, g_trace, (size_t)slots * 32));
+  return CG_OK;
+}

@@ -75,6 +75,25 @@ int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, 
                     uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
                     unsigned long long* best);
 
+// Weight-streaming GEMM for a handful of tokens (M <= 32): y[M, N] = x[M, K] w[N, K]^T on bf16
+// activations.  The gate/up pair can share a CTA with act(gate) * up as the epilogue, and
+// split-K partials are reduced inside a thread-block cluster.
+struct DecGemm {
+  const __nv_bfloat16* x;   // [M, K] activations with row stride ldx
+  int64_t ldx;
+  const __nv_bfloat16* w;   // [w_rows, K] bf16, row stride ldw
+  int64_t ldw, w_rows;
+  void* out;                // [M, N] with row stride ldo
+  int64_t ldo;
+  const float* residual;
+  int out_mode;             // 0: f32, 1: bf16, 2: f32 out = product + residual
+  int dual;                 // 1: rows n and n + N of w form gate and up; out = act(gate) * up
+  int act;                  // 0 silu, 1 tanh-gelu
+  int64_t M, N, K;
+};
+int gemm_dec(cg_ctx* c, const DecGemm& g);
+bool gemm_dec_supported(int64_t M, int64_t K);
+
 // f32 -> bf16 rows (ld in elements for the source)
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out);
 

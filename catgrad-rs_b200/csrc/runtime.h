@@ -62,6 +62,8 @@ struct cg_ctx {
   int64_t launches = 0;
   int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
   int opt_pdl = 1;        // programmatic dependent launch for the fused kernels
+  bool trace_on = false;  // record a device timeline of the decode GEMM launches
+  int64_t trace_next = 0;
   void* comm = nullptr;   // ncclComm_t
   int comm_rank = 0, comm_world = 1;
   // host function pointer of cuTensorMapEncodeTiled, resolved on first use

@@ -271,6 +271,13 @@ int32_t cg_decoder_generate(cg_decoder*, const uint32_t* prompt, int32_t batch, 
 int32_t cg_decoder_time_gemms(cg_decoder*, int32_t batch, int32_t iters, float* ms_per_sweep,
                               int32_t* launches_per_sweep);
 
+/* Diagnostics: a device-side timeline of the decode GEMM launches.  After cg_trace_enable(ctx, 1)
+ * every launch records, in launch order (slot = launch number mod 2048), four globaltimer
+ * stamps in nanoseconds: first CTA started, preceding kernel complete, last accumulator
+ * ready, last CTA finished.  cg_trace_read copies `slots` x 4 values. */
+int32_t cg_trace_enable(cg_ctx*, int32_t on);
+int32_t cg_trace_read(cg_ctx*, uint64_t* out, int32_t slots);
+
 /* --- tensor-parallel communicator (NCCL over NVLink; one process per GPU) --- */
 
 /* Size in bytes of the opaque id rank 0 creates and every rank must receive. */

@@ -116,8 +116,8 @@ def test_batch_rows_are_independent(cuda_bf16):
     """The reference graphs are batch-1; a batched run must equal each row run alone."""
     C = cuda_bf16
     cfg = SMALL
-    prompt = synth.make_tokens(cfg, 3, 17, seed=5)
-    dec = cg.Decoder(C, cfg, max_seq=32, max_batch=3)
+    prompt = synth.make_tokens(cfg, 3, 40, seed=5)  # 120 and 40 tokens: the same GEMM path and k order
+    dec = cg.Decoder(C, cfg, max_seq=64, max_batch=3)
     dec.load(synth.make_weights(cfg, 0))
     batched = dec.generate(prompt, 8)
     for b in range(3):
