@@ -7,10 +7,10 @@
 // order repeat_kv produces.  Masked scores are dropped, which equals adding f32::MIN before
 // the softmax (exp underflows to 0).
 //
-//   prefill: 64-query x 64-key tiles, bf16 mma.sync with f32 accumulation, 4 warps
-//   decode : one query per row; keys are streamed once per kv head for all its query
-//            heads, split over the context; a second kernel merges the splits
+// 64-query x 64-key tiles, bf16 mma.sync with f32 accumulation, 4 warps.  (The one-token
+// decode step has its own fused kernel.)
 #include "kernels.h"
+#include "mma.cuh"
 
 #include <algorithm>
 
@@ -19,28 +19,6 @@ namespace cg {
 namespace {
 
 __device__ __forceinline__ float tanh_sig(float x) { return 2.f / (1.f + __expf(-2.f * x)) - 1.f; }
-
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *(uint32_t*)&v;
-}
 
 // ------------------------------------------------------------------ prefill ----------
 template <int D>
@@ -211,181 +189,6 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
   }
 }
 
-// ------------------------------------------------------------------ decode -----------
-constexpr int DEC_SPLITS = 8;   // context slices per (row, kv head)
-constexpr int MAX_REP = 8;      // query heads per kv head supported by the decode kernel
-
-// scratch layout per (b, h, split): [m, l, o[0..d)]
-template <int D>
-__global__ void __launch_bounds__(128) k_attn_decode(AttnArgs a, float scale, int rep) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  constexpr int E = D / 32;  // output elements per lane
-  __shared__ float qs[MAX_REP][D];
-  __shared__ float ps[4][MAX_REP][32];
-  __shared__ float red_m[4][MAX_REP], red_l[4][MAX_REP];
-  __shared__ float red_o[4][MAX_REP][D];
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvh = blockIdx.x, split = blockIdx.z;
-  const int64_t b = blockIdx.y;
-  const int64_t qp = a.pos_dev ? *a.pos_dev : a.pos0;
-  const int64_t T = qp + 1;  // keys visible to the new token
-  int64_t lo = 0;
-  if (a.window > 0) lo = std::max<int64_t>(0, qp - a.window + 1);
-  const int64_t span = T - lo;
-  const int64_t per = (span + DEC_SPLITS - 1) / DEC_SPLITS;
-  const int64_t t0 = lo + split * per, t1 = std::min<int64_t>(T, t0 + per);
-
-  const __nv_bfloat16* qbase = a.q + b * (int64_t)a.nh * D + (int64_t)kvh * rep * D;
-  for (int i = tid; i < rep * D; i += 128) qs[i / D][i % D] = __bfloat162float(qbase[i]);
-  __syncthreads();
-
-  const __nv_bfloat16* kbase = a.k_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
-  const __nv_bfloat16* vbase = a.v_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
-
-  float m[MAX_REP], l[MAX_REP], o[MAX_REP][E];
-#pragma unroll
-  for (int r = 0; r < MAX_REP; ++r) {
-    m[r] = -INFINITY;
-    l[r] = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) o[r][e] = 0.f;
-  }
-
-  for (int64_t c0 = t0 + warp * 32; c0 < t1; c0 += 4 * 32) {
-    const int64_t j = c0 + lane;
-    const bool valid = j < t1;
-    float sc[MAX_REP];
-#pragma unroll
-    for (int r = 0; r < MAX_REP; ++r) sc[r] = 0.f;
-    if (valid) {
-      const uint4* krow = (const uint4*)(kbase + j * (int64_t)D);
-#pragma unroll 8
-      for (int ch = 0; ch < D / 8; ++ch) {
-        const uint4 kv = krow[ch];
-        const __nv_bfloat162* k2 = (const __nv_bfloat162*)&kv;
-        float kf[8];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 f = __bfloat1622float2(k2[t]);
-          kf[2 * t] = f.x;
-          kf[2 * t + 1] = f.y;
-        }
-#pragma unroll
-        for (int r = 0; r < MAX_REP; ++r) {
-          if (r < rep) {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) sc[r] += qs[r][ch * 8 + t] * kf[t];
-          }
-        }
-      }
-    }
-    float corr[MAX_REP];
-#pragma unroll
-    for (int r = 0; r < MAX_REP; ++r) {
-      if (r < rep) {
-        float v = sc[r] * scale;
-        if (a.softcap > 0.f) v = a.softcap * tanh_sig(v / a.softcap);
-        v = valid ? v : -INFINITY;
-        float mx = v;
-#pragma unroll
-        for (int s = 16; s; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
-        const float mnew = fmaxf(m[r], mx);  // finite: lane 0 of every chunk is valid
-        const float p = __expf(v - mnew);
-        float sum = p;
-#pragma unroll
-        for (int s = 16; s; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
-        corr[r] = __expf(m[r] - mnew);
-        l[r] = l[r] * corr[r] + sum;
-        m[r] = mnew;
-        ps[warp][r][lane] = p;
-      }
-    }
-    __syncwarp();
-#pragma unroll
-    for (int r = 0; r < MAX_REP; ++r)
-      if (r < rep) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) o[r][e] *= corr[r];
-      }
-    // eight value rows per round, all loads issued before the first use; rows past the
-    // slice repeat its last row and carry probability 0
-    constexpr int VU = 8;
-#pragma unroll 1
-    for (int jj = 0; jj < 32; jj += VU) {
-      if (c0 + jj >= t1) break;
-      __nv_bfloat162 vraw[VU][E / 2];
-#pragma unroll
-      for (int u = 0; u < VU; ++u) {
-        const int64_t row = std::min<int64_t>(c0 + jj + u, t1 - 1);
-        const __nv_bfloat162* vrow = (const __nv_bfloat162*)(vbase + row * (int64_t)D + lane * E);
-#pragma unroll
-        for (int e = 0; e < E / 2; ++e) vraw[u][e] = vrow[e];
-      }
-#pragma unroll
-      for (int u = 0; u < VU; ++u) {
-#pragma unroll
-        for (int r = 0; r < MAX_REP; ++r)
-          if (r < rep) {
-            const float p = ps[warp][r][jj + u];
-#pragma unroll
-            for (int e = 0; e < E / 2; ++e) {
-              const float2 f = __bfloat1622float2(vraw[u][e]);
-              o[r][2 * e] += p * f.x;
-              o[r][2 * e + 1] += p * f.y;
-            }
-          }
-      }
-    }
-    __syncwarp();
-  }
-
-  // merge the four warps
-  for (int r = 0; r < rep; ++r) {
-    if (lane == 0) { red_m[warp][r] = m[r]; red_l[warp][r] = l[r]; }
-#pragma unroll
-    for (int e = 0; e < E; ++e) red_o[warp][r][lane * E + e] = o[r][e];
-  }
-  __syncthreads();
-  for (int i = tid; i < rep * D; i += 128) {
-    const int r = i / D, e = i % D;
-    float mm = -INFINITY;
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w][r]);
-    float ll = 0.f, oo = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      const float f = red_m[w][r] == -INFINITY ? 0.f : __expf(red_m[w][r] - mm);
-      ll += red_l[w][r] * f;
-      oo += red_o[w][r][e] * f;
-    }
-    const int h = kvh * rep + r;
-    float* dst = a.scratch + (((b * a.nh + h) * DEC_SPLITS) + split) * (int64_t)(D + 2);
-    if (e == 0) { dst[0] = mm; dst[1] = ll; }
-    dst[2 + e] = oo;
-  }
-}
-
-template <int D>
-__global__ void k_attn_combine(const float* scratch, __nv_bfloat16* out, int nh) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int h = blockIdx.x;
-  const int64_t b = blockIdx.y;
-  const float* src = scratch + ((b * nh + h) * DEC_SPLITS) * (int64_t)(D + 2);
-  float mm = -INFINITY;
-  for (int s = 0; s < DEC_SPLITS; ++s) mm = fmaxf(mm, src[s * (D + 2)]);
-  for (int e = threadIdx.x; e < D; e += blockDim.x) {
-    float ll = 0.f, oo = 0.f;
-    for (int s = 0; s < DEC_SPLITS; ++s) {
-      const float ms = src[s * (D + 2)];
-      const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
-      ll += src[s * (D + 2) + 1] * f;
-      oo += src[s * (D + 2) + 2 + e] * f;
-    }
-    out[(b * nh + h) * (int64_t)D + e] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
-  }
-}
-
 template <int D>
 int launch_prefill(cg_ctx* c, const AttnArgs& a) {
   constexpr size_t smem = (size_t)3 * 64 * (D + 8) * 2;
@@ -401,19 +204,6 @@ int launch_prefill(cg_ctx* c, const AttnArgs& a) {
   return CG_OK;
 }
 
-template <int D>
-int launch_decode(cg_ctx* c, const AttnArgs& a) {
-  const int rep = a.nh / a.nkv;
-  dim3 grid((unsigned)a.nkv, (unsigned)a.B, DEC_SPLITS);
-  const float scale = 1.0f / sqrtf((float)D);
-  CG_CUDA(c, launch_kernel(c, k_attn_decode<D>, grid, dim3(128), 0, 1, a, scale, rep));
-  CG_LAUNCHED(c);
-  dim3 g2((unsigned)a.nh, (unsigned)a.B);
-  CG_CUDA(c, launch_kernel(c, k_attn_combine<D>, g2, dim3(D < 128 ? 64 : 128), 0, 1, (const float*)a.scratch, a.out, a.nh));
-  CG_LAUNCHED(c);
-  return CG_OK;
-}
-
 int check(cg_ctx* c, const AttnArgs& a) {
   if (a.nkv <= 0 || a.nh % a.nkv) return fail(c, CG_ERR_SHAPE, "attention: heads must be a multiple of kv heads");
   if (a.d != 64 && a.d != 128 && a.d != 256) return fail(c, CG_ERR_UNSUPPORTED, "attention: head_dim must be 64, 128 or 256");
@@ -424,8 +214,6 @@ int check(cg_ctx* c, const AttnArgs& a) {
 
 }  // namespace
 
-int64_t attn_decode_scratch_floats(int64_t B, int nh, int d) { return B * nh * DEC_SPLITS * (int64_t)(d + 2); }
-
 int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a) {
   CG_TRY(check(c, a));
   if (a.B == 0 || a.S == 0) return CG_OK;
@@ -433,19 +221,6 @@ int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a) {
     case 64: return launch_prefill<64>(c, a);
     case 128: return launch_prefill<128>(c, a);
     default: return launch_prefill<256>(c, a);
-  }
-}
-
-int k_launch_attn_decode(cg_ctx* c, const AttnArgs& a) {
-  CG_TRY(check(c, a));
-  if (a.S != 1) return fail(c, CG_ERR_INVALID, "attention decode takes one token per row");
-  if (a.nh / a.nkv > MAX_REP) return fail(c, CG_ERR_UNSUPPORTED, "attention decode: more than 8 query heads per kv head");
-  if (!a.scratch) return fail(c, CG_ERR_INVALID, "attention decode needs scratch");
-  if (a.B == 0) return CG_OK;
-  switch (a.d) {
-    case 64: return launch_decode<64>(c, a);
-    case 128: return launch_decode<128>(c, a);
-    default: return launch_decode<256>(c, a);
   }
 }
 

@@ -63,7 +63,8 @@ struct cg_decoder {
   // workspace (sized for `cap` tokens)
   int64_t cap = 0;
   cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *hact = nullptr,
-            *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *attn_scratch = nullptr, *best = nullptr;
+            *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *best = nullptr;
+  int attn_splits = 1;
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
   int64_t step_launches = 0;     // kernels in one decode step
@@ -199,6 +200,27 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                             cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0));
+    const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
+    if (S == 1) {
+      AttnDecArgs f;
+      f.qkv = (const float*)D->qkvb->data();
+      f.cos_t = (const float*)D->cos_t->data();
+      f.sin_t = (const float*)D->sin_t->data();
+      f.q_gamma = L.q_norm ? (const float*)L.q_norm->data() : nullptr;
+      f.k_gamma = L.k_norm ? (const float*)L.k_norm->data() : nullptr;
+      f.norm_eps = cfg.rms_eps;
+      f.norm_plus_one = cfg.norm_plus_one;
+      f.k_cache = (__nv_bfloat16*)L.k_cache->data();
+      f.v_cache = (__nv_bfloat16*)L.v_cache->data();
+      f.out = (__nv_bfloat16*)D->att->data();
+      f.pos_dev = from_dev_pos ? D->pos_dev() : nullptr;
+      f.pos0 = pos0; f.Tmax = cfg.max_seq; f.B = B;
+      f.nh = D->nh; f.nkv = D->nkv; f.d = D->d;
+      f.window = windowed ? cfg.sliding_window : 0;
+      f.softcap = cfg.attn_softcap;
+      f.splits = D->attn_splits;
+      CG_TRY(k_launch_attn_dec(c, f));
+    } else {
     RopeStoreArgs r;
     r.qkv = (const float*)D->qkvb->data();
     r.cos_t = (const float*)D->cos_t->data();
@@ -222,12 +244,11 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     a.B = B; a.S = S; a.pos0 = pos0; a.Tmax = cfg.max_seq;
     a.pos_dev = from_dev_pos ? D->pos_dev() : nullptr;
     a.nh = D->nh; a.nkv = D->nkv; a.d = D->d;
-    const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
     a.window = windowed ? cfg.sliding_window : 0;
     a.softcap = cfg.attn_softcap;
-    a.scratch = (float*)D->attn_scratch->data();
-    if (S == 1) CG_TRY(k_launch_attn_decode(c, a));
-    else CG_TRY(k_launch_attn_prefill(c, a));
+    a.scratch = nullptr;
+    CG_TRY(k_launch_attn_prefill(c, a));
+    }
     CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn));
     CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                             cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
@@ -342,7 +363,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
-  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->attn_scratch); drop(D->best);
+  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best);
   delete D;
   return CG_OK;
 }
@@ -469,8 +490,8 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   n = 2 * (int64_t)cfg.max_batch;  // one 64-bit argmax merge slot per row
   CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->best));
   CG_CUDA(c, cudaMemsetAsync(D->best->data(), 0, (size_t)n * 4, c->core->stream));
-  n = attn_decode_scratch_floats(cfg.max_batch, D->nh, D->d);
-  CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->attn_scratch));
+  D->attn_splits = attn_dec_splits(cfg.max_seq);
+
   CG_TRY(ensure_workspace(D, cfg.max_batch));
   CG_TRY(set_state(D, 0, 0));
   D->finalized = true;

@@ -114,6 +114,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   if (warp == 0) {
     if (lane == 0 && nkb > 0) {
       // weights first: they do not depend on the preceding kernel
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       const int pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i) {
         const uint32_t full = bars + 8 * i;
@@ -238,6 +239,7 @@ int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const De
   static size_t configured = 0;  // largest dynamic shared memory size set so far
   if (smem > configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     configured = smem;
   }
   CG_CUDA(c, launch_kernel(c, k_gemm_dec<TN>, grid, dim3(192), smem, a.splits, mw, mx, a));
@@ -256,10 +258,10 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   const int tn = g.M <= 16 ? 16 : 32;
   const int64_t tiles = (g.N + BM - 1) / BM;
   const int kb_total = (int)((g.K + BK - 1) / BK);
-  // split-K: a power of two up to 8 (one portable cluster), about two CTAs per SM in total,
-  // at least two k blocks per CTA
+  // split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this
+  // GPU supports), about two CTAs per SM in total, at least two k blocks per CTA
   int splits = 1;
-  while (splits < 8 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
+  while (splits < 16 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
   int kb_per = (kb_total + splits - 1) / splits;
   if ((kb_total + kb_per - 1) / kb_per != splits) {  // an empty slice would break the cluster shape
     splits = 1;

@@ -56,14 +56,33 @@ struct AttnArgs {
   int nh, nkv, d;
   int64_t window;                // 0 = none
   float softcap;                 // 0 = none
-  float* scratch;                // decode only: split partials, see attn_decode_scratch_floats
+  float* scratch;                // unused
 };
 // Causal (optionally windowed / soft-capped) attention of S new tokens per row against cache
 // positions [0, pos0 + S).  Tensor-core flash kernel.
 int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a);
-// One new token per row (S == 1): split-KV streaming kernel + combine.
-int k_launch_attn_decode(cg_ctx* c, const AttnArgs& a);
-int64_t attn_decode_scratch_floats(int64_t B, int nh, int d);
+
+struct AttnDecArgs {
+  const float* qkv;              // [B, (nh + 2 nkv) d] f32: the fused projection of the new tokens
+  const float* cos_t;            // rotary tables [Tmax, d/2]
+  const float* sin_t;
+  const float* q_gamma;          // optional per-head norm weights [d] (null = none)
+  const float* k_gamma;
+  float norm_eps;
+  int norm_plus_one;
+  __nv_bfloat16* k_cache;        // [B, nkv, Tmax, d]; position pos is appended
+  __nv_bfloat16* v_cache;
+  __nv_bfloat16* out;            // [B, nh d]
+  const int64_t* pos_dev;        // position of the new token, read on the device when non-null
+  int64_t pos0, Tmax, B;
+  int nh, nkv, d;
+  int64_t window;                // 0 = none
+  float softcap;                 // 0 = none
+  int splits;                    // grid z = cluster size: context slices per (row, kv head)
+};
+// Rope + cache append + attention + merge of one new token per row, in one launch.
+int k_launch_attn_dec(cg_ctx* c, const AttnDecArgs& a);
+int attn_dec_splits(int64_t Tmax);
 
 // tokens[b] = argmax over the vocabulary with the reference's tie rule (last index); optional
 // soft-cap applied to the logits in place first.  The logits are `parts` vocabulary slices of
