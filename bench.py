@@ -191,19 +191,7 @@ def main():
     torch.cuda.set_stream(tstream)
     C = cg.CudaBackend(local, cg.PREC_BF16, stream=tstream.cuda_stream)
     if world > 1:
-        import ctypes
-        L = C._lib
-        n = L.cg_comm_id_size()
-        buf = torch.zeros(n, dtype=torch.uint8)
-        if rank == 0:
-            raw = (ctypes.c_uint8 * n)()
-            assert L.cg_comm_make_id(raw) == 0
-            buf = torch.tensor(list(raw), dtype=torch.uint8)
-        buf = buf.cuda()
-        dist.broadcast(buf, 0)
-        raw = (ctypes.c_uint8 * n)(*buf.cpu().tolist())
-        L.cg_comm_init.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32]
-        C._check(L.cg_comm_init(C._ctx, raw, rank, world))
+        importlib.import_module("catgrad-rs_b200.tp").init_comm(C, rank, world)
 
     dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=B, tp_rank=rank, tp_world=world)
     dec.load(synth.make_weights(cfg, 0))

@@ -7,11 +7,12 @@ The directory name is not a Python identifier; import it with
 * `graphs`   — the op streams of catgrad's stdlib and catgrad-llm model graphs
 * `decoder`  — the fused, KV-cached greedy runner
 * `synth`    — seeded synthetic checkpoints and prompts
+* `tp`       — tensor-parallel sharding plan and communicator set-up
 * `build`    — the nvcc recipe for libcatgrad_cuda.so
 """
 from .backend import (  # noqa: F401
     F32, U32, PREC_F32, PREC_BF16, BackendError, BackendPanic, TaggedTensor, TraitBackend,
     CudaBackend, load_library, library_path,
 )
-from . import graphs, synth  # noqa: F401
+from . import graphs, synth, tp  # noqa: F401
 from .decoder import Decoder, DecoderConfig  # noqa: F401

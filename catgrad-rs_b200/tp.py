@@ -1,0 +1,54 @@
+"""Tensor parallelism of the decoder over the GPUs of one node: one process per GPU.
+
+The model shards where it does naturally (attention heads and FFN columns are independent
+until the output projections, the vocabulary until the arg-max):
+
+* q/k/v projections: rows of the rank's heads            (column parallel)
+* o projection:      columns of the rank's heads         (row parallel  -> all-reduce)
+* gate/up:           rows of the rank's FFN slice        (column parallel)
+* down:              columns of the rank's FFN slice     (row parallel  -> all-reduce)
+* LM head:           rows of the rank's vocabulary slice (all-gather of logits, then arg-max)
+
+`shard_plan` is the index arithmetic (the native decoder applies the same ranges when it
+keeps its shard of the full tensors it is handed); `init_comm` carries the NCCL unique id
+from rank 0 to the others through torch.distributed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+
+def shard_plan(cfg, rank: int, world: int) -> dict:
+    """Row/column ranges (start, stop) of every sharded parameter for `rank` of `world`."""
+    nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.get_head_dim()
+    F, V = cfg.intermediate_size, cfg.vocab_size
+    if nh % world or nkv % world or F % world or V % world:
+        raise ValueError("heads, kv heads, ffn and vocab must divide by the tensor-parallel degree")
+    q = (rank * (nh // world) * d, (rank + 1) * (nh // world) * d)
+    kv = (rank * (nkv // world) * d, (rank + 1) * (nkv // world) * d)
+    f = (rank * (F // world), (rank + 1) * (F // world))
+    v = (rank * (V // world), (rank + 1) * (V // world))
+    return {"q_rows": q, "kv_rows": kv, "o_cols": q, "ffn_rows": f, "down_cols": f, "vocab_rows": v}
+
+
+def init_comm(backend, rank: int, world: int) -> None:
+    """Create the library's NCCL communicator on `backend` (collective over all ranks).
+    torch.distributed must already be initialised; it only moves the 128-byte id."""
+    import torch
+    import torch.distributed as dist
+
+    L = backend._lib
+    L.cg_comm_id_size.restype = C.c_int32
+    L.cg_comm_make_id.argtypes = [C.c_void_p]
+    L.cg_comm_init.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]
+    n = L.cg_comm_id_size()
+    raw = (C.c_uint8 * n)()
+    if rank == 0:
+        if L.cg_comm_make_id(raw) != 0:
+            raise RuntimeError("cg_comm_make_id failed")
+    buf = torch.tensor(list(raw), dtype=torch.uint8)
+    if dist.get_backend() == "nccl":
+        buf = buf.cuda()
+    dist.broadcast(buf, 0)
+    raw = (C.c_uint8 * n)(*buf.cpu().tolist())
+    backend._check(L.cg_comm_init(backend._ctx, raw, int(rank), int(world)))
