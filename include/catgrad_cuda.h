@@ -278,6 +278,21 @@ int32_t cg_decoder_time_gemms(cg_decoder*, int32_t batch, int32_t iters, float* 
 int32_t cg_trace_enable(cg_ctx*, int32_t on);
 int32_t cg_trace_read(cg_ctx*, uint64_t* out, int32_t slots);
 
+/* Row-wise arg-max for callers that cannot allocate device memory (code that runs while
+ * another stream of the process is being captured into a CUDA graph, plugins with a fixed memory
+ * budget, latency-critical loops).  It has no counterpart in the reference: it is the arg-max of
+ * cg_argmax (ties -> last index, IEEE total order) on raw device pointers, with its per-row
+ * merge slots in a fixed array inside the library instead of memory from an allocator.
+ *   logits : device, f32 [rows, n] contiguous      out : device, u32 [rows]
+ *   rows <= CG_NOALLOC_MAX_ROWS, else CG_ERR_INVALID with a message in `err` (optional buffer).
+ * The call enqueues on `stream` (a cudaStream_t, NULL = default stream) of the CURRENT device and
+ * calls no cudaMalloc / cudaFree.  The first call on a device resolves the array's device
+ * address; make it before any stream capture.  All calls share the array: calls that overlap
+ * on the GPU race; calls on one stream are safe. */
+#define CG_NOALLOC_MAX_ROWS 4096
+int32_t cg_argmax_rows_noalloc(void* stream, const float* logits, int64_t rows, int64_t n, uint32_t* out,
+                               char* err, int64_t err_cap);
+
 /* --- tensor-parallel communicator (NCCL over NVLink; one process per GPU) --- */
 
 /* Size in bytes of the opaque id rank 0 creates and every rank must receive. */
