@@ -100,6 +100,21 @@ __global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* ou
   const int64_t m = blockIdx.y;
   const float* g = gu + m * 2 * F;
   const float* u = g + F;
+  if ((F & 3) == 0) {
+    // 128-bit loads, 64-bit stores
+    const float4* g4 = (const float4*)g;
+    const float4* u4 = (const float4*)u;
+    uint2* o2 = (uint2*)(out + m * F);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < F / 4; i += (int64_t)gridDim.x * blockDim.x) {
+      const float4 a = g4[i], b = u4[i];
+      float r[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = act == 0 ? silu_f(r[j]) : gelu_f(r[j]);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r[0] * b.x, r[1] * b.y), hi = __floats2bfloat162_rn(r[2] * b.z, r[3] * b.w);
+      o2[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    }
+    return;
+  }
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < F; i += (int64_t)gridDim.x * blockDim.x) {
     const float a = act == 0 ? silu_f(g[i]) : gelu_f(g[i]);
     out[m * F + i] = __float2bfloat16_rn(a * u[i]);
@@ -309,7 +324,7 @@ int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float ep
 
 int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out) {
   if (M == 0 || F == 0) return CG_OK;
-  dim3 grid((unsigned)std::min<int64_t>((F + 255) / 256, 64), (unsigned)M);
+  dim3 grid((unsigned)std::min<int64_t>((F / 4 + 255) / 256 + 1, 64), (unsigned)M);
   CG_CUDA(c, launch_kernel(c, k_act_mul, grid, dim3(256), 0, 1, gu, F, act, out));
   CG_LAUNCHED(c);
   return CG_OK;

@@ -174,13 +174,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
         for (int j = 0; j < 16; ++j) stage[(c0 + j) * BM + row] = __uint_as_float(v[j]);
       } else if (n < p.N) {
+        if (p.splits == 1 && p.out_mode == 2) {
+          // out may alias residual, so the compiler cannot move a load above the previous
+          // store: issue all 16 residual loads first, then the stores
+          float res[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + c0 + j;
-          if (m >= p.M) break;
-          const float acc = __uint_as_float(v[j]);
-          if (p.splits > 1) p.partial[((int64_t)split * p.M + m) * p.N + n] = acc;
-          else store_out(p, m, n, acc);
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            res[j] = m < p.M ? p.residual[(int64_t)m * p.ldo + n] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < p.M) ((float*)p.out)[(int64_t)m * p.ldo + n] = __uint_as_float(v[j]) + res[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m >= p.M) break;
+            const float acc = __uint_as_float(v[j]);
+            if (p.splits > 1) p.partial[((int64_t)split * p.M + m) * p.N + n] = acc;
+            else store_out(p, m, n, acc);
+          }
         }
       }
     }
