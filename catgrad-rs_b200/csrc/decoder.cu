@@ -178,11 +178,11 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
   if (!tp && !post_norm) return gemm(D, xin, M, w, x, x, 2);
   float* t = (float*)D->tmp->data();
   if (tp && !post_norm) {
-    // rank 0 folds the residual into its partial; the sum over ranks is the new x everywhere
-    CG_TRY(gemm(D, xin, M, w, t, x, D->cfg.tp_rank == 0 ? 2 : 0));
-    CG_TRY(all_reduce_f32(D, t, M * D->H));
-    CG_CUDA(c, cudaMemcpyAsync(x, t, (size_t)M * D->H * 4, cudaMemcpyDeviceToDevice, c->core->stream));
-    return CG_OK;
+    // in place: rank 0 leaves x + partial in x, every other rank just its partial (its copy of
+    // the old x is identical to rank 0's and no longer needed); the sum over ranks is the new
+    // residual stream on every rank
+    CG_TRY(gemm(D, xin, M, w, x, x, D->cfg.tp_rank == 0 ? 2 : 0));
+    return all_reduce_f32(D, x, M * D->H);
   }
   CG_TRY(gemm(D, xin, M, w, t, nullptr, 0));
   CG_TRY(all_reduce_f32(D, t, M * D->H));

@@ -67,6 +67,22 @@ class Decoder:
         c.max_batch = max_batch
         c.tp_rank = tp_rank
         c.tp_world = tp_world
+        arch = getattr(cfg, "arch", "llama")
+        if arch == "qwen3":
+            c.arch = 1
+            c.qk_norm = 1
+        elif arch == "gemma":
+            c.arch = 2
+            c.act = 1
+            c.norm_plus_one = 1
+            c.post_norms = 1
+            c.embed_scale = float(np.sqrt(np.float32(cfg.hidden_size), dtype=np.float32))
+            c.tie_embeddings = 1
+            c.qk_norm = int(cfg.qk_norm)
+            c.attn_softcap = cfg.attn_logit_softcap
+            c.final_softcap = cfg.final_logit_softcap
+            c.sliding_window = cfg.sliding_window
+            c.window_every = 2
         for k, v in switches.items():
             setattr(c, k, v)
         self.cfg = c

@@ -28,6 +28,19 @@ class ModelConfig:
     rope_theta: float = 10000.0
     tie_word_embeddings: bool = False
     dtype: str = "f32"
+    arch: str = "llama"               # "llama" | "qwen3" | "gemma"
+    # qwen3 (catgrad-llm/src/models/qwen3.rs)
+    num_local_experts: int = 0        # > 1: mixture-of-experts FFN on sparse layers
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = False
+    decoder_sparse_step: int = 1
+    # gemma (catgrad-llm/src/models/gemma3.rs graph; the soft-caps and the window are the
+    # Gemma-2 additions of BASELINE config 3, composed from reference ops)
+    qk_norm: bool = False             # per-head q/k RMSNorm (qwen3 always, gemma3 yes, gemma-2 no)
+    attn_logit_softcap: float = 0.0
+    final_logit_softcap: float = 0.0
+    sliding_window: int = 0           # 0 = none; even layers use it when set
     extras: dict = field(default_factory=dict)
 
     def __post_init__(self):
@@ -48,7 +61,9 @@ LLAMA_3_8B = ModelConfig("llama-3-8b-shape", 4096, 14336, 32, 32, 8, 128256, rms
 
 
 def param_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
-    """Hugging Face tensor names and shapes of a Llama checkpoint (all weights [out, in])."""
+    """Hugging Face tensor names and shapes of a checkpoint (all weights [out, in]); experts are
+    already stacked [E, ...] the way the reference driver stacks them
+    (catgrad-llm/examples/llama/main.rs:173-264)."""
     H, F, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
     nh, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
     shapes = {"model.embed_tokens.weight": (cfg.vocab_size, H), "model.norm.weight": (H,)}
@@ -62,9 +77,23 @@ def param_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
         shapes[p + "self_attn.k_proj.weight"] = (nkv * d, H)
         shapes[p + "self_attn.v_proj.weight"] = (nkv * d, H)
         shapes[p + "self_attn.o_proj.weight"] = (H, nh * d)
-        shapes[p + "mlp.gate_proj.weight"] = (F, H)
-        shapes[p + "mlp.up_proj.weight"] = (F, H)
-        shapes[p + "mlp.down_proj.weight"] = (H, F)
+        if cfg.qk_norm or cfg.arch == "qwen3":
+            shapes[p + "self_attn.q_norm.weight"] = (d,)
+            shapes[p + "self_attn.k_norm.weight"] = (d,)
+        if cfg.arch == "gemma":
+            shapes[p + "pre_feedforward_layernorm.weight"] = (H,)
+            shapes[p + "post_feedforward_layernorm.weight"] = (H,)
+        moe = cfg.num_local_experts > 1 and (i + 1) % cfg.decoder_sparse_step == 0
+        if moe:
+            E, Fe = cfg.num_local_experts, cfg.moe_intermediate_size
+            shapes[p + "mlp.gate.weight"] = (E, H)
+            shapes[p + "mlp.experts.gate_proj.weight"] = (E, Fe, H)
+            shapes[p + "mlp.experts.up_proj.weight"] = (E, Fe, H)
+            shapes[p + "mlp.experts.down_proj.weight"] = (E, H, Fe)
+        else:
+            shapes[p + "mlp.gate_proj.weight"] = (F, H)
+            shapes[p + "mlp.up_proj.weight"] = (F, H)
+            shapes[p + "mlp.down_proj.weight"] = (H, F)
     return shapes
 
 
@@ -83,7 +112,8 @@ def make_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02):
     for name in sorted(shapes):
         shp = shapes[name]
         if len(shp) == 1:
-            w = np.ones(shp, dtype=np.float32)
+            # norm gains: an effective gain of 1 (gemma multiplies by 1 + gamma, so gamma = 0)
+            w = np.zeros(shp, dtype=np.float32) if cfg.arch == "gemma" else np.ones(shp, dtype=np.float32)
         else:
             w = rng.standard_normal(shp, dtype=np.float32) * np.float32(std)
             if cfg.dtype == "bf16":
