@@ -333,6 +333,7 @@ class CudaBackend(TraitBackend):
             ("cg_fused_rope", [vp, vp, f32, i64, out], i32),
             ("cg_fused_attention", [vp, vp, vp, vp, i64, f32, out], i32),
             ("cg_linear", [vp, vp, vp, out], i32),
+            ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
         ]:
             fn = getattr(L, name)
             fn.argtypes = args
@@ -390,3 +391,10 @@ class CudaBackend(TraitBackend):
 
     def linear(self, x, w):
         return self._ext1("cg_linear", x._h, w._h)
+
+    def fused_moe(self, x, router, gate, up, down, top_k, norm_topk=True, act=0):
+        """(out, expert ids) of the mixture-of-experts block (qwen3.rs:64-133) on normalised rows."""
+        o, ids = _c_vp(), _c_vp()
+        self._check(self._lib.cg_fused_moe(self._ctx, x._h, router._h, gate._h, up._h, down._h, int(top_k),
+                                           int(norm_topk), int(act), C.byref(o), C.byref(ids)))
+        return self._wrap(o), self._wrap(ids)

@@ -15,6 +15,8 @@
 //   w_o     [ H, nh d ]           bf16
 //   w_gu    [ 2 F, H ]            bf16   rows = gate, then up
 //   w_down  [ H, F ]              bf16
+//   experts [ E / W ][ Fe, H ] x2, [ E / W ][ H, Fe ] bf16 on mixture-of-experts layers (whole
+//           experts per rank), router [ E, H ] f32
 //   embed   [ V, H ]              bf16   (also the LM head when tied)
 //   k/v     [ L ][ B, nkv, Tmax, d ] bf16
 //   x       [ M, H ] f32 residual stream; bf16 only where a tensor-core GEMM reads it
@@ -35,6 +37,9 @@ struct Layer {
   cg_tensor *ln_in = nullptr, *ln_post_attn = nullptr, *ln_pre_ffn = nullptr, *ln_post_ffn = nullptr;
   cg_tensor *q_norm = nullptr, *k_norm = nullptr;
   cg_tensor *k_cache = nullptr, *v_cache = nullptr;
+  // mixture-of-experts layers (qwen3.rs:64-133): router [E, H] f32, this rank's experts stacked
+  bool moe = false;
+  cg_tensor *router = nullptr, *we_gate = nullptr, *we_up = nullptr, *we_down = nullptr;
 };
 
 void drop(cg_tensor*& t) {
@@ -64,6 +69,10 @@ struct cg_decoder {
   int64_t cap = 0;
   cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *hact = nullptr,
             *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *best = nullptr;
+  // mixture-of-experts scratch, sized for cap * top_k pairs
+  cg_tensor *m_ids = nullptr, *m_wts = nullptr, *m_pos = nullptr, *m_tiles = nullptr, *m_xg = nullptr, *m_h = nullptr,
+            *m_y = nullptr;
+  int El = 0;                    // experts on this rank
   int attn_splits = 1;
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
@@ -75,6 +84,8 @@ struct cg_decoder {
 };
 
 namespace {
+
+int all_reduce_f32(cg_decoder* D, float* p, int64_t n);
 
 int get_param(cg_decoder* D, const std::string& name, cg_tensor** out, bool required = true) {
   auto it = D->params.find(name);
@@ -130,8 +141,60 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->gu));
   s2[1] = D->F;
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->hact));
+  if (D->cfg.n_experts > 0) {
+    drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
+    const int64_t P = M * D->cfg.top_k;
+    int64_t n = P;
+    CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->m_ids));
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->m_wts));
+    CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->m_pos));
+    n = 3 * P + 4;
+    CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->m_tiles));
+    s2[0] = P; s2[1] = H;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->m_xg));
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->m_y));
+    s2[1] = D->cfg.moe_ffn;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->m_h));
+    // rows of a tile past its group are computed and discarded: keep them finite
+    CG_CUDA(c, cudaMemsetAsync(D->m_xg->data(), 0, (size_t)P * H * 2, c->core->stream));
+    CG_CUDA(c, cudaMemsetAsync(D->m_h->data(), 0, (size_t)P * D->cfg.moe_ffn * 2, c->core->stream));
+  }
   D->cap = M;
   return CG_OK;
+}
+
+// The expert block of layer L on M tokens; under tensor parallelism every rank owns whole
+// experts and the partial sums meet in the all-reduce of the residual stream.
+int moe_block(cg_decoder* D, Layer& L, int64_t M) {
+  const cg_decoder_config& cfg = D->cfg;
+  const int64_t P = M * cfg.top_k;
+  MoeArgs a;
+  a.x = (const float*)D->x->data();
+  a.out = (float*)D->x->data();
+  a.gamma = (const float*)L.ln_pre_ffn->data();
+  a.eps = cfg.rms_eps;
+  a.plus_one = cfg.norm_plus_one;
+  a.router = (const float*)L.router->data();
+  a.w_gate = (const __nv_bfloat16*)L.we_gate->data();
+  a.w_up = (const __nv_bfloat16*)L.we_up->data();
+  a.w_down = (const __nv_bfloat16*)L.we_down->data();
+  a.H = (int)D->H; a.E = cfg.n_experts; a.k = cfg.top_k; a.Fe = cfg.moe_ffn; a.norm_topk = cfg.norm_topk; a.act = cfg.act;
+  a.e_lo = cfg.tp_rank * D->El; a.El = D->El;
+  a.add_residual = cfg.tp_world > 1 && cfg.tp_rank != 0 ? 0 : 1;
+  a.M = M;
+  a.xn = (__nv_bfloat16*)D->xn->data();
+  int32_t* t = (int32_t*)D->m_tiles->data();
+  const int64_t Pc = D->cap * cfg.top_k;
+  a.w.ids = (uint32_t*)D->m_ids->data();
+  a.w.wts = (float*)D->m_wts->data();
+  a.w.pos = (int32_t*)D->m_pos->data();
+  a.w.tile_expert = t; a.w.tile_row0 = t + Pc; a.w.tile_rows = t + 2 * Pc; a.w.n_tiles = t + 3 * Pc;
+  a.w.xg = (__nv_bfloat16*)D->m_xg->data();
+  a.w.h = (__nv_bfloat16*)D->m_h->data();
+  a.w.y = (float*)D->m_y->data();
+  (void)P;
+  CG_TRY(moe_ffn(D->c, a));
+  return all_reduce_f32(D, (float*)D->x->data(), M * D->H);
 }
 
 // y = x W^T (+ residual) on bf16 activations.  mode: 0 -> f32 out, 1 -> bf16 out,
@@ -250,6 +313,10 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     CG_TRY(k_launch_attn_prefill(c, a));
     }
     CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn));
+    if (L.moe) {
+      CG_TRY(moe_block(D, L, M));
+      continue;
+    }
     CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                             cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     if (small) {
@@ -327,8 +394,14 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
   if (k.num_layers <= 0 || k.hidden <= 0 || k.n_heads <= 0 || k.n_kv_heads <= 0 || k.head_dim <= 0 || k.ffn <= 0 ||
       k.vocab <= 0 || k.max_seq <= 0 || k.max_batch <= 0)
     return fail(c, CG_ERR_INVALID, "decoder: sizes must be positive");
-  if (k.n_experts > 0) return fail(c, CG_ERR_UNSUPPORTED, "decoder: mixture-of-experts layers are not built yet");
   const int W = k.tp_world < 1 ? 1 : k.tp_world;
+  if (k.n_experts > 0) {
+    if (k.top_k < 1 || k.top_k > 32 || k.top_k > k.n_experts || k.moe_ffn <= 0 || k.moe_ffn % 8 || k.n_experts % W)
+      return fail(c, CG_ERR_UNSUPPORTED,
+                  "decoder: experts per token must be in [1, 32], the expert width a multiple of 8, experts divisible by the "
+                  "parallel degree");
+    if (k.post_norms) return fail(c, CG_ERR_UNSUPPORTED, "decoder: expert layers with post-norms are not supported");
+  }
   if (k.tp_rank < 0 || k.tp_rank >= W) return fail(c, CG_ERR_INVALID, "decoder: tp_rank out of range");
   if (k.n_heads % k.n_kv_heads || k.n_heads % W || k.n_kv_heads % W || k.ffn % W || k.vocab % W)
     return fail(c, CG_ERR_SHAPE, "decoder: heads, kv heads, ffn and vocab must divide by the tensor-parallel degree");
@@ -346,6 +419,7 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
   D->F = k.ffn / W;
   D->Vp = k.vocab / W;
   D->qkv = (D->nh + 2 * D->nkv) * D->d;
+  D->El = k.n_experts > 0 ? k.n_experts / W : 0;
   *out = D;
   return CG_OK;
 }
@@ -359,11 +433,13 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
     drop(L.w_qkv); drop(L.w_o); drop(L.w_gu); drop(L.w_down); drop(L.ln_in); drop(L.ln_post_attn);
     if (L.ln_pre_ffn) drop(L.ln_pre_ffn);
     drop(L.ln_post_ffn); drop(L.q_norm); drop(L.k_norm); drop(L.k_cache); drop(L.v_cache);
+    drop(L.router); drop(L.we_gate); drop(L.we_up); drop(L.we_down);
   }
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
   drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best);
+  drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
   delete D;
   return CG_OK;
 }
@@ -390,14 +466,42 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   for (int li = 0; li < cfg.num_layers; ++li) {
     Layer& L = D->layers[li];
     const std::string p = "model.layers." + std::to_string(li) + ".";
-    cg_tensor *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    cg_tensor *wq, *wk, *wv, *wo, *wg = nullptr, *wu = nullptr, *wd = nullptr, *wr = nullptr;
     CG_TRY(get_param(D, p + "self_attn.q_proj.weight", &wq));
     CG_TRY(get_param(D, p + "self_attn.k_proj.weight", &wk));
     CG_TRY(get_param(D, p + "self_attn.v_proj.weight", &wv));
     CG_TRY(get_param(D, p + "self_attn.o_proj.weight", &wo));
-    CG_TRY(get_param(D, p + "mlp.gate_proj.weight", &wg));
-    CG_TRY(get_param(D, p + "mlp.up_proj.weight", &wu));
-    CG_TRY(get_param(D, p + "mlp.down_proj.weight", &wd));
+    // a layer is sparse when the checkpoint has a router for it (qwen3.rs:297-298)
+    if (cfg.n_experts > 0) CG_TRY(get_param(D, p + "mlp.gate.weight", &wr, false));
+    L.moe = wr != nullptr;
+    if (L.moe) {
+      const int64_t E = cfg.n_experts, Fe = cfg.moe_ffn, El = D->El;
+      cg_tensor *eg, *eu, *ed;
+      CG_TRY(get_param(D, p + "mlp.experts.gate_proj.weight", &eg));
+      CG_TRY(get_param(D, p + "mlp.experts.up_proj.weight", &eu));
+      CG_TRY(get_param(D, p + "mlp.experts.down_proj.weight", &ed));
+      if (wr->rank != 2 || wr->dims[0] != E || wr->dims[1] != H || eg->rank != 3 || eg->dims[0] != E || eg->dims[1] != Fe ||
+          eg->dims[2] != H || eu->rank != 3 || eu->dims[0] != E || eu->dims[1] != Fe || eu->dims[2] != H || ed->rank != 3 ||
+          ed->dims[0] != E || ed->dims[1] != H || ed->dims[2] != Fe)
+        return fail(c, CG_ERR_SHAPE, "decoder: expert parameters have unexpected shapes");
+      CG_TRY(as_contiguous_f32(c, wr, &L.router));
+      for (auto pr : {std::make_pair(eg, &L.we_gate), std::make_pair(eu, &L.we_up), std::make_pair(ed, &L.we_down)}) {
+        cg_tensor* sl = nullptr;
+        CG_TRY(cg_slice(c, pr.first, 0, (int64_t)R * El, El, &sl));
+        Hold hs(sl);
+        if (sl->storage == ST_BF16 && sl->contiguous()) { sl->rc++; *pr.second = sl; }  // already in the layout the GEMM reads
+        else CG_TRY(cg_to_bf16(c, sl, pr.second));
+      }
+      for (const char* n : {"mlp.gate.weight", "mlp.experts.gate_proj.weight", "mlp.experts.up_proj.weight",
+                            "mlp.experts.down_proj.weight"}) {
+        auto it = D->params.find(p + n);
+        if (it != D->params.end()) { release(it->second); D->params.erase(it); }
+      }
+    } else {
+      CG_TRY(get_param(D, p + "mlp.gate_proj.weight", &wg));
+      CG_TRY(get_param(D, p + "mlp.up_proj.weight", &wu));
+      CG_TRY(get_param(D, p + "mlp.down_proj.weight", &wd));
+    }
     if (wq->rank != 2 || wq->dims[0] != nh_all * d || wk->rank != 2 || wk->dims[0] != nkv_all * d || wv->rank != 2 ||
         wv->dims[0] != nkv_all * d)
       return fail(c, CG_ERR_SHAPE, "decoder: attention projections have unexpected shapes");
@@ -409,13 +513,15 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
     s2[0] = H; s2[1] = D->nh * d;
     CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_o));
     CG_TRY(copy_block(c, wo, 0, H, (int64_t)R * D->nh * d, D->nh * d, L.w_o, 0));
-    s2[0] = 2 * (int64_t)D->F; s2[1] = H;
-    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_gu));
-    CG_TRY(copy_block(c, wg, (int64_t)R * D->F, D->F, 0, H, L.w_gu, 0));
-    CG_TRY(copy_block(c, wu, (int64_t)R * D->F, D->F, 0, H, L.w_gu, D->F));
-    s2[0] = H; s2[1] = D->F;
-    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_down));
-    CG_TRY(copy_block(c, wd, 0, H, (int64_t)R * D->F, D->F, L.w_down, 0));
+    if (!L.moe) {
+      s2[0] = 2 * (int64_t)D->F; s2[1] = H;
+      CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_gu));
+      CG_TRY(copy_block(c, wg, (int64_t)R * D->F, D->F, 0, H, L.w_gu, 0));
+      CG_TRY(copy_block(c, wu, (int64_t)R * D->F, D->F, 0, H, L.w_gu, D->F));
+      s2[0] = H; s2[1] = D->F;
+      CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_down));
+      CG_TRY(copy_block(c, wd, 0, H, (int64_t)R * D->F, D->F, L.w_down, 0));
+    }
     CG_TRY(norm_weight(D, p + "input_layernorm.weight", H, &L.ln_in));
     if (cfg.post_norms) {
       // four norms per layer (catgrad-llm/src/models/gemma3.rs:192-238)
@@ -612,6 +718,7 @@ int32_t cg_decoder_time_gemms(cg_decoder* D, int32_t batch, int32_t iters, float
       Layer& L = D->layers[li];
       st = gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0);
       if (st == CG_OK) st = gemm(D, D->att, M, L.w_o, D->tmp->data(), nullptr, 0);
+      if (L.moe) continue;  // the expert GEMMs depend on the routing: not part of this sweep
       if (st == CG_OK) st = small ? gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 1, true)
                                   : gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0);
       if (st == CG_OK) st = gemm(D, D->hact, M, L.w_down, D->tmp->data(), nullptr, 0);

@@ -113,6 +113,37 @@ struct DecGemm {
 int gemm_dec(cg_ctx* c, const DecGemm& g);
 bool gemm_dec_supported(int64_t M, int64_t K);
 
+// Mixture-of-experts feed-forward block (catgrad-llm/src/models/qwen3.rs:64-133) on M tokens:
+// x += sum over the top-k experts of weight * down(act(gate(xn)) * up(xn)), xn = rmsnorm(x).
+struct MoeWork {              // device scratch for up to `pairs` (token, slot) pairs
+  uint32_t* ids;              // [pairs] expert of each pair, token-major
+  float* wts;                 // [pairs] routing weight of each pair
+  int32_t* pos;               // [pairs] row of the pair in grouped order, -1 = not on this rank
+  int32_t *tile_expert, *tile_row0, *tile_rows, *n_tiles;  // GEMM tile list ([pairs] each, one count)
+  __nv_bfloat16* xg;          // [pairs, H] activations in grouped order
+  __nv_bfloat16* h;           // [pairs, Fe]
+  float* y;                   // [pairs, H]
+};
+struct MoeArgs {
+  const float* x;             // [M, H] input rows (the residual stream)
+  float* out;                 // [M, H] result; may be x
+  const float* gamma;         // norm weights [H]; null = x is used as it is
+  float eps;
+  int plus_one;
+  const float* router;        // [E, H] f32
+  const __nv_bfloat16 *w_gate, *w_up;  // [El, Fe, H] experts this rank owns
+  const __nv_bfloat16* w_down;         // [El, H, Fe]
+  int H, E, k, Fe, norm_topk, act;
+  int e_lo, El;               // this rank owns experts [e_lo, e_lo + El)
+  int add_residual;           // 1: out = x + expert sum; 0: out = this rank's expert sum only
+  int64_t M;
+  __nv_bfloat16* xn;          // [M, H] scratch: the normalised rows
+  MoeWork w;
+};
+int moe_ffn(cg_ctx* c, const MoeArgs& a);
+int moe_pick_tn(int64_t pairs, int experts);
+int64_t moe_max_tiles(int64_t pairs, int experts_local, int tn);
+
 // f32 -> bf16 rows (ld in elements for the source)
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out);
 

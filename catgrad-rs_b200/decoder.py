@@ -83,6 +83,12 @@ class Decoder:
             c.final_softcap = cfg.final_logit_softcap
             c.sliding_window = cfg.sliding_window
             c.window_every = 2
+        if getattr(cfg, "num_local_experts", 0) > 1:
+            # mixture-of-experts FFN on the layers whose checkpoint carries a router (qwen3.rs:297-298)
+            c.n_experts = cfg.num_local_experts
+            c.top_k = cfg.num_experts_per_tok
+            c.moe_ffn = cfg.moe_intermediate_size
+            c.norm_topk = int(cfg.norm_topk_prob)
         for k, v in switches.items():
             setattr(c, k, v)
         self.cfg = c

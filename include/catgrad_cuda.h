@@ -197,6 +197,16 @@ int32_t cg_fused_attention(cg_ctx*, const cg_tensor* q, const cg_tensor* k, cons
  * (linear_no_bias, nn/mod.rs:174-199), without materialising the transpose.  Uses the
  * tcgen05 kernel when W is stored bf16. */
 int32_t cg_linear(cg_ctx*, const cg_tensor* x, const cg_tensor* w, cg_tensor** out);
+/* The mixture-of-experts block of catgrad-llm/src/models/qwen3.rs:64-133 on rows x [.., H]
+ * (already normalised): softmax(x router^T) -> top_k experts per row (ties -> lower id, as
+ * Backend::topk) -> weights renormalised to sum 1 when norm_topk != 0 -> out = sum over the
+ * chosen experts (in slot order) of weight * down_e(act(gate_e x) * up_e x).  router [E, H],
+ * gate/up [E, F, H], down [E, H, F] as the checkpoints stack them.  The expert matmuls run on
+ * the tensor cores with bf16 operands; routing is f32.  ids_out (optional) receives the chosen
+ * expert ids [rows, top_k] U32. */
+int32_t cg_fused_moe(cg_ctx*, const cg_tensor* x, const cg_tensor* router, const cg_tensor* gate,
+                     const cg_tensor* up, const cg_tensor* down, int32_t top_k, int32_t norm_topk,
+                     int32_t act, cg_tensor** out, cg_tensor** ids_out);
 
 /* --- decoder runner: the greedy loop of catgrad-llm/examples/llama/main.rs:118-169 with a
  * device KV cache (cache semantics of catgrad-llm/src/legacy/models/utils.rs:210-228). --- */

@@ -57,7 +57,7 @@ def test_op_stream_parity_f32(oracle, cuda, cfg):
         np.testing.assert_array_equal(a, b)   # top-k expert ids: bit-exact
 
 
-@pytest.mark.parametrize("cfg", [QWEN_DENSE, GEMMA2, GEMMA3], ids=lambda c: c.name)
+@pytest.mark.parametrize("cfg", [QWEN_DENSE, QWEN_MOE, GEMMA2, GEMMA3], ids=lambda c: c.name)
 def test_decoder_switches_match_checker(oracle, cuda_bf16, cfg):
     import dataclasses
     cfg = dataclasses.replace(cfg, dtype="bf16")
