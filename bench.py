@@ -93,6 +93,29 @@ class ClockSampler:
         return out
 
 
+# name -> (model shape in synth, batch, prompt, decode steps)
+WORKLOADS = {
+    "llama1b": ("LLAMA_32_1B", 8, 512, 128),
+    "llama1b-b1": ("LLAMA_32_1B", 1, 512, 128),
+    "gemma2": ("GEMMA_2_2B", 4, 2048, 128),
+    "qwen3moe": ("QWEN3_30B_A3B", 8, 1024, 64),
+    "llama8b": ("LLAMA_3_8B", 32, 4096, 256),
+}
+
+
+def dense_params_per_step(cfg) -> int:
+    """Weights every decode step streams whatever the routing: all dense linear layers and the LM
+    head (expert matrices are excluded: how many a step touches depends on the router)."""
+    H, F, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nh, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    total = cfg.vocab_size * H
+    for i in range(cfg.num_hidden_layers):
+        total += H * (nh * d) + 2 * H * (nkv * d) + (nh * d) * H
+        sparse = cfg.num_local_experts > 1 and (i + 1) % cfg.decoder_sparse_step == 0
+        total += cfg.num_local_experts * H if sparse else 3 * H * F
+    return total
+
+
 def reference_job_seconds(t_forward: float, prompt: int, decode: int, batch: int) -> float:
     """Cost of the whole job on the reference's driver from one measured forward of `prompt`
     tokens: every generated token is a full forward over all tokens so far
@@ -133,9 +156,12 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--workload", default="llama1b", choices=sorted(WORKLOADS),
+                    help="llama1b is the configuration the metric is quoted on; the others are the remaining "
+                         "model shapes at their own batch / prompt / decode sizes")
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--prompt", type=int, default=0)
+    ap.add_argument("--decode", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="a 4-layer model of the same widths (profiling captures)")
     args = ap.parse_args()
@@ -145,7 +171,10 @@ def main():
     cg = importlib.import_module("catgrad-rs_b200")
     synth = cg.synth
     import dataclasses
-    cfg = synth.LLAMA_32_1B
+    cfg_name, B0, S0, T0 = WORKLOADS[args.workload]
+    cfg = getattr(synth, cfg_name)
+    args.batch, args.prompt, args.decode = args.batch or B0, args.prompt or S0, args.decode or T0
+    headline = args.workload == "llama1b"
     if args.small:
         cfg = dataclasses.replace(cfg, name=cfg.name + "-4layer", num_hidden_layers=4)
     B, S, T = args.batch, args.prompt, args.decode
@@ -194,7 +223,12 @@ def main():
         importlib.import_module("catgrad-rs_b200.tp").init_comm(C, rank, world)
 
     dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=B, tp_rank=rank, tp_world=world)
-    dec.load(synth.make_weights(cfg, 0))
+    if headline:
+        dec.load(synth.make_weights(cfg, 0))
+        generator = f"numpy {np.__version__} PCG64, weights seed 0 N(0,0.02) rounded to bf16, ids seed 1"
+    else:
+        dec.load_random(cfg, 0)  # tens of GB: drawn on the device instead of crossing the host link
+        generator = "weights N(0,0.02) from the library's counter-based device generator (seed 0), ids numpy PCG64 seed 1"
     prompt = synth.make_tokens(cfg, B, S, seed=1)
     prompt_dev = C.from_numpy(prompt)
     C.sync()
@@ -249,8 +283,15 @@ def main():
     ms_decode = timed(lambda: dec.decode(T - 1), 1) / max(T - 1, 1)
     gemm_ms, gemm_launches = dec.time_gemms(B, 20)
     peak, peak_kind = measured_peaks()
-    weight_bytes = 2 * synth.linear_params_per_token(cfg) / world
+    weight_bytes = 2 * dense_params_per_step(cfg) / world
     kv_bytes = B * synth.kv_bytes_per_token(cfg) * (S + T / 2) / world
+    expert_bytes = 0.0
+    if cfg.num_local_experts > 1:
+        # expected distinct experts a step of B tokens touches under uniform routing, per sparse layer
+        E, k = cfg.num_local_experts, cfg.num_experts_per_tok
+        distinct = E * (1.0 - (1.0 - 1.0 / E) ** (B * k))
+        sparse_layers = sum(1 for i in range(cfg.num_hidden_layers) if (i + 1) % cfg.decoder_sparse_step == 0)
+        expert_bytes = sparse_layers * distinct * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2 / world
     achieved = weight_bytes / (gemm_ms * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -266,21 +307,23 @@ def main():
         "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": f"tp{world}",
                    "l2": "inputs larger than L2: every decode step streams the full weight set "
                          f"({weight_bytes / 1e9:.2f} GB per GPU) plus the KV cache",
-                   "generator": f"numpy {np.__version__} PCG64, weights seed 0 N(0,0.02) rounded to bf16, ids seed 1"},
+                   "generator": generator},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(prompt.nbytes),
                 "d2h_bytes_per_step": int(B * (T + 1) * 4)},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": "k_gemm_tc<16,10> + k_splitk_reduce: all weight-streaming GEMMs of one decode step",
+        "roofline": {"bound": "hbm", "kernel": "k_gemm_dec (k_gemm_tc for the LM head): all dense weight-streaming GEMMs of one decode step",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                      "traffic": traffic, "algorithmic_bytes_per_sweep": weight_bytes, "launches_per_sweep": gemm_launches,
                      "ms_per_sweep": gemm_ms},
         "phases": {"prefill_ms": ms_prefill, "prefill_tok_s": B * S / (ms_prefill * 1e-3),
                    "decode_ms_per_step": ms_decode, "decode_tok_s": B / (ms_decode * 1e-3),
-                   "decode_step_hbm_floor_ms": (weight_bytes + kv_bytes) / (peak * 1e9) * 1e3,
-                   "decode_step_frac_of_hbm_roofline": (weight_bytes + kv_bytes) / (peak * 1e9) * 1e3 / ms_decode},
+                   "decode_step_hbm_floor_ms": (weight_bytes + kv_bytes + expert_bytes) / (peak * 1e9) * 1e3,
+                   "decode_step_frac_of_hbm_roofline": (weight_bytes + kv_bytes + expert_bytes) / (peak * 1e9) * 1e3 / ms_decode,
+                   "decode_step_bytes": {"dense_weights": weight_bytes, "kv_cache": kv_bytes,
+                                         "experts_expected": expert_bytes}},
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and headline:
         forward, cores = run_reference_sample(cg, dataclasses.replace(cfg, dtype="bf16"), S)
         t_fwd = forward()
         job = reference_job_seconds(t_fwd, S, T, B)

@@ -334,6 +334,7 @@ class CudaBackend(TraitBackend):
             ("cg_fused_attention", [vp, vp, vp, vp, i64, f32, out], i32),
             ("cg_linear", [vp, vp, vp, out], i32),
             ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
+            ("cg_randn", [vp, _c_i64p, i32, C.c_uint64, f32, f32, out], i32),
         ]:
             fn = getattr(L, name)
             fn.argtypes = args
@@ -391,6 +392,11 @@ class CudaBackend(TraitBackend):
 
     def linear(self, x, w):
         return self._ext1("cg_linear", x._h, w._h)
+
+    def randn(self, shape, seed, std=1.0, mean=0.0):
+        """N(mean, std) samples generated on the device (cg_randn)."""
+        dims = (C.c_int64 * max(1, len(shape)))(*shape)
+        return self._ext1("cg_randn", dims, len(shape), C.c_uint64(seed), C.c_float(mean), C.c_float(std))
 
     def fused_moe(self, x, router, gate, up, down, top_k, norm_topk=True, act=0):
         """(out, expert ids) of the mixture-of-experts block (qwen3.rs:64-133) on normalised rows."""

@@ -216,7 +216,9 @@ int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, voi
     g.M = M; g.N = N; g.K = K;
     return gemm_dec(D->c, g);
   }
-  if (dual) return fail(D->c, CG_ERR_INVALID, "decoder: the fused gate/up epilogue is a decode-path feature");
+  if (dual)
+    return gemm_tc_pair(D->c, (const __nv_bfloat16*)xin->data(), K, (const __nv_bfloat16*)w->data(), K, (__nv_bfloat16*)out, N, M,
+                        N, K, D->cfg.act);
   const int splits = gemm_tc_pick_splits(M, N, K);
   float* ws = (int64_t)splits * M * N <= D->splitk_floats ? (float*)D->splitk->data() : nullptr;
   return gemm_tc(D->c, (const __nv_bfloat16*)xin->data(), K, (const __nv_bfloat16*)w->data(), K, out, N, residual, M, N, K,
@@ -319,13 +321,9 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     }
     CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                             cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
-    if (small) {
-      // gate/up projections and act(gate) * up in one kernel
-      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
-    } else {
-      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0));
-      CG_TRY(k_launch_act_mul(c, (const float*)D->gu->data(), M, D->F, cfg.act, (__nv_bfloat16*)D->hact->data()));
-    }
+    // gate/up projections and act(gate) * up in one kernel
+    CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
+    (void)small;
     CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn));
   }
   return CG_OK;

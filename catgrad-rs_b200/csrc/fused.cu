@@ -292,6 +292,29 @@ __global__ void k_to_bf16(const float* x, int64_t n, __nv_bfloat16* out) {
     out[i] = __float2bfloat16_rn(x[i]);
 }
 
+// Pairs of N(mean, std) samples from a counter-based generator: splitmix64 of (seed, pair
+// index) gives two 24-bit uniforms, Box-Muller turns them into two normals.
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+template <typename T>
+__global__ void k_randn(uint64_t seed, int64_t n, float mean, float std, T* out) {
+  const int64_t pairs = (n + 1) / 2;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t h = mix64(seed ^ mix64((uint64_t)i));
+    const float u1 = (float)((h >> 40) + 1) * (1.0f / 16777216.0f);       // (0, 1]
+    const float u2 = (float)(h & 0xFFFFFFull) * (1.0f / 16777216.0f);     // [0, 1)
+    const float r = sqrtf(-2.0f * logf(u1)) * std;
+    float sn, cs;
+    sincosf(6.283185307179586f * u2, &sn, &cs);
+    out[2 * i] = (T)(mean + r * cs);
+    if (2 * i + 1 < n) out[2 * i + 1] = (T)(mean + r * sn);
+  }
+}
+
 }  // namespace
 
 int k_launch_embed(cg_ctx* c, const uint32_t* tokens, int64_t tok_ld, int64_t tok_off, int64_t S, const void* table, int st,
@@ -498,6 +521,23 @@ int32_t cg_linear(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, cg_tensor**
     wv.t->rank = 2; wv.t->dims[0] = K; wv.t->dims[1] = N; wv.t->strides[0] = w->strides[1]; wv.t->strides[1] = w->strides[0];
     rv.t->rank = 2; rv.t->dims[0] = M; rv.t->dims[1] = N; rv.t->strides[0] = N; rv.t->strides[1] = 1;
     CG_TRY(gemm_simt(c, xv.t, wv.t, rv.t));
+  }
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_randn(cg_ctx* c, const int64_t* dims, int32_t rank, uint64_t seed, float mean, float std, cg_tensor** out) {
+  if (!c || !out || rank < 0 || rank > CG_MAX_RANK || (rank && !dims)) return fail(c, CG_ERR_INVALID, "bad argument");
+  // same storage rule as an upload: matrices are kept in bf16 by a bf16-precision context
+  const int st = c->precision == CG_PREC_BF16 && rank >= 2 ? ST_BF16 : ST_F32;
+  Hold r;
+  CG_TRY(new_tensor(c, CG_F32, st, dims, rank, &r.t));
+  const int64_t n = r.t->numel();
+  if (n) {
+    const unsigned grid = grid_for((n + 1) / 2, 256);
+    if (st == ST_BF16) k_randn<<<grid, 256, 0, c->core->stream>>>(seed, n, mean, std, (__nv_bfloat16*)r.t->data());
+    else k_randn<<<grid, 256, 0, c->core->stream>>>(seed, n, mean, std, (float*)r.t->data());
+    CG_LAUNCHED(c);
   }
   *out = r.take();
   return CG_OK;

@@ -29,6 +29,7 @@
 // context's error word, still passes its cluster barriers, frees its TMEM and returns.
 #include <algorithm>
 
+#include "act.cuh"
 #include "tc_common.cuh"
 
 namespace cg {
@@ -46,6 +47,11 @@ struct TcArgs {
   int out_mode;  // 0 f32, 1 bf16, 2 f32 + residual
   int kb_total, kb_per_split, splits;
   int cluster;   // 1: the splits of a tile are one cluster and reduce over shared memory
+  // two accumulators per CTA (ACC2 kernels): the second weight tile starts row2_off rows below
+  // the first and both multiply the same activation tile
+  int n_stride;  // weight rows between consecutive CTAs along x (128, or 256 for a 256-row tile)
+  int row2_off;  // 128: one 256-row tile; N: gate and up rows paired
+  int pair_act;  // -1: store both accumulators; 0 / 1: out = act(first) * second in bf16 (silu / tanh-gelu)
   int32_t* err;
 };
 
@@ -56,12 +62,13 @@ __device__ __forceinline__ void store_out(const TcArgs& p, int m, int n, float a
   else ((float*)p.out)[o] = acc + p.residual[o];
 }
 
-template <int TN, int STAGES, int MINB>
+template <int TN, int STAGES, int MINB, int ACC2>
 __global__ void __launch_bounds__(192, MINB)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs p) {
   constexpr uint32_t B_BYTES = TN * BK * 2;
-  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t NCOLS = TN < 32 ? 32 : TN;  // TMEM columns: power of two >= 32
+  constexpr uint32_t W_BYTES = A_BYTES * (1 + ACC2);
+  constexpr uint32_t STAGE_BYTES = W_BYTES + B_BYTES;
+  constexpr uint32_t NCOLS = TN * (1 + ACC2) < 32 ? 32 : TN * (1 + ACC2);  // TMEM columns: power of two >= 32
 
   // the next kernel in the stream may start its own prologue now
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -76,7 +83,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   volatile int* cta_abort = (volatile int*)(gen + STAGES * STAGE_BYTES + 16 * STAGES + 12);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * TN, split = blockIdx.z;
+  const int n0 = blockIdx.x * (ACC2 ? p.n_stride : BM), m0 = blockIdx.y * TN, split = blockIdx.z;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
   const int nkb = kb1 - kb0;
@@ -109,8 +116,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const int pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i) {
         const uint32_t full = bars + 8 * i;
-        mbar_expect_tx(full, A_BYTES);
+        mbar_expect_tx(full, W_BYTES);
         tma_load_2d(base + i * STAGE_BYTES, &map_w, (kb0 + i) * BK, n0, full);
+        if (ACC2) tma_load_2d(base + i * STAGE_BYTES + A_BYTES, &map_w, (kb0 + i) * BK, n0 + p.row2_off, full);
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < nkb; ++i) {
@@ -121,11 +129,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         if (i >= pre) {
           const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
           if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
-          mbar_expect_tx(full, A_BYTES);
+          mbar_expect_tx(full, W_BYTES);
           tma_load_2d(a, &map_w, k, n0, full);
+          if (ACC2) tma_load_2d(a + A_BYTES, &map_w, k, n0 + p.row2_off, full);
         }
         mbar_expect_tx(full, B_BYTES);
-        tma_load_2d(a + A_BYTES, &map_x, k, m0, full);
+        tma_load_2d(a + W_BYTES, &map_x, k, m0, full);
       }
     }
   } else if (warp == 1) {
@@ -142,8 +151,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
           const uint64_t da = umma_desc(a + kk * UMMA_K * 2);
-          const uint64_t db = umma_desc(a + A_BYTES + kk * UMMA_K * 2);
+          const uint64_t db = umma_desc(a + W_BYTES + kk * UMMA_K * 2);
           umma_bf16(tmem_acc, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          if (ACC2) umma_bf16(tmem_acc + TN, umma_desc(a + A_BYTES + kk * UMMA_K * 2), db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(bars + 8 * (STAGES + s));  // slot reusable once these MMAs have read it
       }
@@ -169,6 +179,50 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       if (m0 + c0 >= p.M) break;
       uint32_t v[16];
       tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+      if (ACC2) {
+        // splits == 1 here: the two accumulators go straight to the output
+        uint32_t u[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(TN + c0), u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (p.pair_act >= 0) {
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c0 + j;
+              if (m >= p.M) break;
+              const float g = __uint_as_float(v[j]);
+              const float h = (p.pair_act == 0 ? silu_f(g) : gelu_f(g)) * __uint_as_float(u[j]);
+              ((__nv_bfloat16*)p.out)[(int64_t)m * p.ldo + n] = __float2bfloat16_rn(h);
+            }
+          }
+        } else {
+          const int n2 = n + p.row2_off;
+          float res[16], res2[16];
+          if (p.out_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c0 + j;
+              res[j] = (m < p.M && n < p.N) ? p.residual[(int64_t)m * p.ldo + n] : 0.f;
+              res2[j] = (m < p.M && n2 < p.N) ? p.residual[(int64_t)m * p.ldo + n2] : 0.f;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m >= p.M) break;
+            const float a1 = __uint_as_float(v[j]), a2 = __uint_as_float(u[j]);
+            const int64_t o = (int64_t)m * p.ldo;
+            if (p.out_mode == 1) {
+              if (n < p.N) ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(a1);
+              if (n2 < p.N) ((__nv_bfloat16*)p.out)[o + n2] = __float2bfloat16_rn(a2);
+            } else {
+              if (n < p.N) ((float*)p.out)[o + n] = p.out_mode == 2 ? a1 + res[j] : a1;
+              if (n2 < p.N) ((float*)p.out)[o + n2] = p.out_mode == 2 ? a2 + res2[j] : a2;
+            }
+          }
+        }
+        continue;
+      }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       if (p.cluster) {
 #pragma unroll
@@ -250,15 +304,15 @@ __global__ void k_splitk_reduce(const float* partial, int splits, int64_t M, int
   }
 }
 
-template <int TN, int STAGES, int MINB>
+template <int TN, int STAGES, int MINB, int ACC2 = 0>
 int launch(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid) {
-  constexpr size_t smem = (size_t)STAGES * (A_BYTES + TN * BK * 2) + 1024 + 16 * STAGES + 64;
+  constexpr size_t smem = (size_t)STAGES * (A_BYTES * (1 + ACC2) + TN * BK * 2) + 1024 + 16 * STAGES + 64;
   static bool configured = false;  // per instantiation; the attribute is per function and device-wide
   if (!configured) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES, MINB, ACC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  CG_CUDA(c, launch_kernel(c, k_gemm_tc<TN, STAGES, MINB>, grid, dim3(192), smem, a.cluster ? a.splits : 1, mw, mx, a));
+  CG_CUDA(c, launch_kernel(c, k_gemm_tc<TN, STAGES, MINB, ACC2>, grid, dim3(192), smem, a.cluster ? a.splits : 1, mw, mx, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -276,6 +330,29 @@ int gemm_tc_pick_splits(int64_t M, int64_t N, int64_t K) {
   int s = 1;
   while (s < 8 && tiles * (s * 2) <= 2 * 148 + 32 && kb / (s * 2) >= 2) s *= 2;
   return s;
+}
+
+int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, __nv_bfloat16* out,
+                 int64_t ldo, int64_t M, int64_t F, int64_t K, int act) {
+  if (M <= 0 || F <= 0) return CG_OK;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+    return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: k and leading dimensions must be multiples of 8, bases 16-byte aligned");
+  if (M > 2147483647ll / 2 || F > 2147483647ll / 4) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: problem too large");
+  const int tn = M <= 128 ? 128 : 256;
+  CUtensorMap mw, mx;
+  CG_TRY(make_map(c, &mw, w, 2 * F, K, ldw, BM));
+  CG_TRY(make_map(c, &mx, x, M, K, ldx, tn));
+  TcArgs a{};
+  a.out = out; a.residual = nullptr; a.partial = nullptr; a.ldo = ldo;
+  a.M = (int)M; a.N = (int)F; a.K = (int)K; a.out_mode = 1;
+  a.kb_total = (int)((K + BK - 1) / BK); a.kb_per_split = a.kb_total; a.splits = 1; a.cluster = 0;
+  a.n_stride = BM; a.row2_off = (int)F; a.pair_act = act;
+  a.err = c->core->dev_err;
+  dim3 grid((unsigned)((F + BM - 1) / BM), (unsigned)((M + tn - 1) / tn), 1);
+  if (grid.y > 65535) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: too many token tiles");
+  if (tn == 128) CG_TRY((launch<128, 4, 1, 1>(c, mw, mx, a, grid)));
+  else CG_TRY((launch<256, 3, 1, 1>(c, mw, mx, a, grid)));
+  return CG_OK;
 }
 
 int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, void* out, int64_t ldo,
@@ -317,9 +394,19 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
   a.kb_per_split = kb_per;
   a.splits = splits;
   a.cluster = cluster ? 1 : 0;
+  a.n_stride = BM; a.row2_off = BM; a.pair_act = -1;
   a.err = c->core->dev_err;
   dim3 grid((unsigned)((N + BM - 1) / BM), (unsigned)((M + tn - 1) / tn), (unsigned)splits);
   if (grid.y > 65535) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: too many token tiles");
+  // large problems: 256 weight rows per CTA in two accumulators, so every activation tile read
+  // from L2 feeds twice the math; only while that still leaves a tile for every SM
+  if (splits == 1 && tn >= 128 && ((N + 2 * BM - 1) / (2 * BM)) * (int64_t)grid.y >= 148) {
+    a.n_stride = 2 * BM;
+    grid.x = (unsigned)((N + 2 * BM - 1) / (2 * BM));
+    if (tn == 128) CG_TRY((launch<128, 4, 1, 1>(c, mw, mx, a, grid)));
+    else CG_TRY((launch<256, 3, 1, 1>(c, mw, mx, a, grid)));
+    return CG_OK;
+  }
   switch (tn) {
     case 16: CG_TRY((launch<16, 6, 2>(c, mw, mx, a, grid))); break;
     case 32: CG_TRY((launch<32, 5, 2>(c, mw, mx, a, grid))); break;

@@ -202,6 +202,10 @@ inline int grid_for(int64_t n, int block, int max_blocks = 148 * 16) {
 int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,
             void* out, int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K,
             int out_mode, int splits, float* workspace);
+// Gate and up projections with the activation fused: w holds the gate rows then the up rows
+// ([2 F, K]); out[M, F] (bf16) = act(x gate^T) * (x up^T), act 0 = silu, 1 = tanh-gelu.
+int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,
+                 __nv_bfloat16* out, int64_t ldo, int64_t M, int64_t F, int64_t K, int act);
 // How many split-K slices gemm_tc would pick for this problem.
 int gemm_tc_pick_splits(int64_t M, int64_t N, int64_t K);
 

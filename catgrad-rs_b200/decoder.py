@@ -116,6 +116,22 @@ class Decoder:
             self.set_param(name, self.B.from_numpy(w))
         self.finalize()
 
+    def load_random(self, cfg, seed: int = 0, std: float = 0.02):
+        """A synthetic checkpoint generated on the device: matrices ~ N(0, std), norm gains 1
+        (0 where the architecture adds 1).  For models whose weights would take minutes to
+        draw and upload from the host; the values differ from `synth.make_weights`."""
+        from . import synth
+        import zlib
+        gain = 0.0 if getattr(cfg, "arch", "llama") == "gemma" else 1.0
+        for name, shape in synth.param_shapes(cfg).items():
+            if len(shape) == 1:
+                t = self.B.randn(shape, 0, std=0.0, mean=gain)
+            else:
+                t = self.B.randn(shape, (seed << 32) ^ zlib.crc32(name.encode()), std=std)
+            self.set_param(name, t)
+            del t
+        self.finalize()
+
     def finalize(self):
         self.B._check(self.B._lib.cg_decoder_finalize(self._h))
 

@@ -60,6 +60,15 @@ LLAMA_3_8B = ModelConfig("llama-3-8b-shape", 4096, 14336, 32, 32, 8, 128256, rms
                          rope_theta=500000.0, tie_word_embeddings=False, dtype="bf16")
 
 
+GEMMA_2_2B = ModelConfig("gemma-2-2b-shape", 2304, 9216, 26, 8, 4, 256000, head_dim=256, rms_norm_eps=1e-6,
+                         rope_theta=10000.0, tie_word_embeddings=True, dtype="bf16", arch="gemma",
+                         attn_logit_softcap=50.0, final_logit_softcap=30.0, sliding_window=4096)
+QWEN3_30B_A3B = ModelConfig("qwen3-30b-a3b-shape", 2048, 6144, 48, 32, 4, 151936, head_dim=128, rms_norm_eps=1e-6,
+                            rope_theta=1e6, tie_word_embeddings=False, dtype="bf16", arch="qwen3",
+                            num_local_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
+                            norm_topk_prob=True)
+
+
 def param_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
     """Hugging Face tensor names and shapes of a checkpoint (all weights [out, in]); experts are
     already stacked [E, ...] the way the reference driver stacks them

@@ -197,6 +197,13 @@ int32_t cg_fused_attention(cg_ctx*, const cg_tensor* q, const cg_tensor* k, cons
  * (linear_no_bias, nn/mod.rs:174-199), without materialising the transpose.  Uses the
  * tcgen05 kernel when W is stored bf16. */
 int32_t cg_linear(cg_ctx*, const cg_tensor* x, const cg_tensor* w, cg_tensor** out);
+/* A tensor of independent N(mean, std) samples generated on the device (counter-based, a
+ * function of seed and element index only).  Stored like an upload of the same shape (bf16
+ * for rank >= 2 under CG_PREC_BF16).  No counterpart in the reference, whose weights always
+ * come from a checkpoint; this exists so that multi-gigabyte synthetic checkpoints need not
+ * cross the host link. */
+int32_t cg_randn(cg_ctx*, const int64_t* dims, int32_t rank, uint64_t seed, float mean, float std,
+                 cg_tensor** out);
 /* The mixture-of-experts block of catgrad-llm/src/models/qwen3.rs:64-133 on rows x [.., H]
  * (already normalised): softmax(x router^T) -> top_k experts per row (ties -> lower id, as
  * Backend::topk) -> weights renormalised to sum 1 when norm_topk != 0 -> out = sum over the

@@ -80,6 +80,30 @@ def test_decoder_matches_checker(oracle, cuda_bf16, cfg, batch, seq, steps):
     dec.close()
 
 
+WIDE = synth.ModelConfig("wide-llama-bf16", 2048, 4096, 1, 32, 8, 512, rms_norm_eps=1e-5, rope_theta=500000.0,
+                         tie_word_embeddings=True, dtype="bf16")
+
+
+def test_wide_prefill_matches_checker(oracle, cuda_bf16):
+    """A prompt batch large enough (7104 tokens per chunk, 2048-wide projections) that the
+    prefill GEMMs take their 256-row two-accumulator tiles, including the residual epilogue and
+    the paired gate/up epilogue."""
+    C, cfg, batch, seq = cuda_bf16, WIDE, 37, 256
+    po = load(oracle, cfg)
+    dec = cg.Decoder(C, cfg, max_seq=seq + 2, max_batch=batch)
+    dec.load(synth.make_weights(cfg, 0))
+    prompt = synth.make_tokens(cfg, batch, seq, seed=3)
+    lg = C.to_numpy(dec.prefill(C.from_numpy(prompt), want_logits=True))
+    for b in (0, 17, 36):
+        want = checker_logits(oracle, cfg, po, prompt[b])[-1]
+        # this model's logits are several times larger than the small models' (2048-wide tied
+        # embedding): the bound is 1% of the logit scale rather than 2e-2 absolute
+        scale = float(np.abs(want).max())
+        assert np.abs(lg[b] - want).max() <= 1e-2 * max(scale, 2.0), (b, float(np.abs(lg[b] - want).max()), scale)
+        assert int(np.argmax(lg[b])) == int(np.argmax(want)) or np.sort(want)[-1] - np.sort(want)[-2] < 2e-2 * scale
+    dec.close()
+
+
 def test_cached_decode_equals_recompute_and_graph_replay(cuda_bf16):
     """Size-independent property: prefill(n) + k cached steps == prefill(n + k) on the tokens
     the decoder itself generated; the captured-graph replay gives the eager step's tokens."""
