@@ -221,6 +221,9 @@ def main():
     C = cg.CudaBackend(local, cg.PREC_BF16, stream=tstream.cuda_stream)
     if world > 1:
         importlib.import_module("catgrad-rs_b200.tp").init_comm(C, rank, world)
+        mapped, why = C.peer_exchange()
+        collective = "decode: partial products pushed over mapped peer memory, no collective call; prefill: NCCL" if mapped \
+            else "NCCL all-reduce / all-gather (peer mapping unavailable: " + why + ")"
 
     dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=B, tp_rank=rank, tp_world=world)
     if headline:
@@ -305,6 +308,7 @@ def main():
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": f"tp{world}",
+                   **({"tp_collective": collective} if world > 1 else {}),
                    "l2": "inputs larger than L2: every decode step streams the full weight set "
                          f"({weight_bytes / 1e9:.2f} GB per GPU) plus the KV cache",
                    "generator": generator},

@@ -393,6 +393,16 @@ class CudaBackend(TraitBackend):
     def linear(self, x, w):
         return self._ext1("cg_linear", x._h, w._h)
 
+    def peer_exchange(self):
+        """(mapped, reason): whether decode-step reductions run over mapped peer memory
+        (cg_comm_peer_exchange) after `tp.init_comm`."""
+        fn = self._lib.cg_comm_peer_exchange
+        fn.argtypes = [_c_vp, C.c_char_p, C.c_int64]
+        fn.restype = C.c_int32
+        buf = C.create_string_buffer(256)
+        ok = fn(self._ctx, buf, 256)
+        return bool(ok), buf.value.decode()
+
     def randn(self, shape, seed, std=1.0, mean=0.0):
         """N(mean, std) samples generated on the device (cg_randn)."""
         dims = (C.c_int64 * max(1, len(shape)))(*shape)

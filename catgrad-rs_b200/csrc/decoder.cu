@@ -74,6 +74,8 @@ struct cg_decoder {
             *m_y = nullptr;
   int El = 0;                    // experts on this rank
   int attn_splits = 1;
+  bool pending_reduce = false;   // x still lacks the addends pushed by the last row-parallel GEMM
+  bool logits_gathered = true;   // `logits` holds every rank's slice
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
   int64_t step_launches = 0;     // kernels in one decode step
@@ -86,6 +88,7 @@ struct cg_decoder {
 namespace {
 
 int all_reduce_f32(cg_decoder* D, float* p, int64_t n);
+bool use_push(cg_decoder* D, int64_t M, int64_t S);
 
 int get_param(cg_decoder* D, const std::string& name, cg_tensor** out, bool required = true) {
   auto it = D->params.find(name);
@@ -212,6 +215,9 @@ int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, voi
     g.x = (const __nv_bfloat16*)xin->data(); g.ldx = K;
     g.w = (const __nv_bfloat16*)w->data(); g.ldw = K; g.w_rows = w->dims[0];
     g.out = out; g.ldo = N; g.residual = residual; g.out_mode = mode;
+    PeerPush px;
+    g.push = nullptr;
+    if (mode == 3) { px = peer_push_of(D->c->xchg); g.push = &px; }
     g.dual = dual ? 1 : 0; g.act = D->cfg.act;
     g.M = M; g.N = N; g.K = K;
     return gemm_dec(D->c, g);
@@ -236,10 +242,13 @@ int all_reduce_f32(cg_decoder* D, float* p, int64_t n) {
 
 // x += W-projection of `xin` (row-split under tensor parallelism), optionally through a
 // post-norm: x += rmsnorm(proj).
-int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm) {
+int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm, bool push) {
   cg_ctx* c = D->c;
   const bool tp = D->cfg.tp_world > 1;
   float* x = (float*)D->x->data();
+  // decode under tensor parallelism: the GEMM pushes its partial product to every rank and
+  // the norm that follows adds the partials of all ranks to x (no collective call)
+  if (push) return gemm(D, xin, M, w, nullptr, nullptr, 3);
   if (!tp && !post_norm) return gemm(D, xin, M, w, x, x, 2);
   float* t = (float*)D->tmp->data();
   if (tp && !post_norm) {
@@ -254,16 +263,32 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
   return k_launch_rmsnorm_add(c, t, (const float*)post_norm->data(), D->cfg.rms_eps, D->cfg.norm_plus_one, M, D->H, x);
 }
 
+// The library-free reduction path serves decode steps of dense pre-norm models when the
+// ranks could map each other's exchange areas.
+bool use_push(cg_decoder* D, int64_t M, int64_t S) {
+  const cg_decoder_config& cfg = D->cfg;
+  return cfg.tp_world > 1 && D->c->xchg.ok && D->c->opt_peer && S == 1 && small_m(M, D->H) && !cfg.post_norms &&
+         cfg.n_experts == 0 && M * D->H <= D->c->xchg.max_elems;
+}
+
 // All layers for M = B * S new tokens at positions [pos0, pos0 + S); x holds the embeddings.
 int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_pos) {
   cg_ctx* c = D->c;
   const cg_decoder_config& cfg = D->cfg;
   const int64_t M = B * S;
+  const bool push = use_push(D, M, S);
+  const PeerPush px = push ? peer_push_of(c->xchg) : PeerPush{};
+  D->pending_reduce = false;
   for (int li = 0; li < cfg.num_layers; ++li) {
     Layer& L = D->layers[li];
     const bool small = small_m(M, D->H);
-    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
-                            cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    if (D->pending_reduce)
+      CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
+                                     cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    else
+      CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
+                              cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    D->pending_reduce = false;
     CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0));
     const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
     if (S == 1) {
@@ -314,7 +339,15 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     a.scratch = nullptr;
     CG_TRY(k_launch_attn_prefill(c, a));
     }
-    CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn));
+    CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push));
+    if (push) {
+      CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
+                                     cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
+      CG_TRY(project_add(D, D->hact, M, L.w_down, nullptr, true));
+      D->pending_reduce = true;
+      continue;
+    }
     if (L.moe) {
       CG_TRY(moe_block(D, L, M));
       continue;
@@ -324,7 +357,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     // gate/up projections and act(gate) * up in one kernel
     CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
     (void)small;
-    CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn));
+    CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn, false));
   }
   return CG_OK;
 }
@@ -333,11 +366,24 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
 int run_head(cg_decoder* D, int64_t B, int64_t S, bool advance) {
   cg_ctx* c = D->c;
   const cg_decoder_config& cfg = D->cfg;
-  CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data() + (S - 1) * D->H, S * D->H, (const float*)D->ln_f->data(),
-                          cfg.rms_eps, cfg.norm_plus_one, B, D->H, D->xl->data(), 1));
   float* lg = (float*)D->logits->data();
   float* mine = lg + (int64_t)cfg.tp_rank * B * D->Vp;
+  if (D->pending_reduce) {
+    // decode step on the push path: S == 1
+    const PeerPush px = peer_push_of(c->xchg);
+    CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)D->ln_f->data(), cfg.rms_eps,
+                                   cfg.norm_plus_one, B, D->H, D->xl->data(), 1));
+    D->pending_reduce = false;
+    CG_TRY(gemm(D, D->xl, B, D->head, mine, nullptr, 0));
+    D->logits_gathered = false;
+    return k_launch_argmax_tp(c, px, mine, B, D->Vp, cfg.final_softcap, (uint32_t*)D->cur->data(),
+                              (uint32_t*)D->history->data(), cfg.max_seq, D->count_dev(), D->pos_dev(), advance ? 1 : 0,
+                              (unsigned long long*)D->best->data());
+  }
+  CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data() + (S - 1) * D->H, S * D->H, (const float*)D->ln_f->data(),
+                          cfg.rms_eps, cfg.norm_plus_one, B, D->H, D->xl->data(), 1));
   CG_TRY(gemm(D, D->xl, B, D->head, mine, nullptr, 0));
+  D->logits_gathered = true;
   if (cfg.tp_world > 1) {
     if (!c->comm) return fail(c, CG_ERR_COMM, "decoder: tensor parallelism needs cg_comm_init first");
     ncclResult_t r = nccl().AllGather(mine, lg, (size_t)(B * D->Vp), ncclFloat32, (ncclComm_t)c->comm, c->core->stream);
@@ -361,6 +407,14 @@ int logits_copy(cg_decoder* D, cg_tensor** out) {
   if (!out) return CG_OK;
   cg_ctx* c = D->c;
   const int W = D->cfg.tp_world;
+  if (W > 1 && !D->logits_gathered) {
+    // the push path leaves every rank with its own vocabulary slice only
+    float* lg = (float*)D->logits->data();
+    ncclResult_t r = nccl().AllGather(lg + (int64_t)D->cfg.tp_rank * D->B * D->Vp, lg, (size_t)(D->B * D->Vp), ncclFloat32,
+                                      (ncclComm_t)c->comm, c->core->stream);
+    if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllGather: ") + nccl().GetErrorString(r));
+    D->logits_gathered = true;
+  }
   int64_t od[2] = {D->B, (int64_t)D->Vp * W};
   Hold r;
   CG_TRY(new_tensor(c, CG_F32, ST_F32, od, 2, &r.t));

@@ -230,7 +230,8 @@ __global__ void k_rope_store(RopeStoreArgs a) {
 // (key << 32 | index) and merges it into best[row] with a 64-bit atomic max, which is
 // order-independent and therefore deterministic; a one-block kernel then publishes the
 // tokens.  An optional soft-cap is written back to the logits first.
-__global__ void k_argmax_part(float* logits, int64_t B, int64_t Vp, int parts, float softcap, unsigned long long* best_out) {
+__global__ void k_argmax_part(float* logits, int64_t B, int64_t Vp, int parts, float softcap, unsigned long long* best_out,
+                              uint32_t idx_off) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ unsigned long long sh[32];
@@ -246,7 +247,7 @@ __global__ void k_argmax_part(float* logits, int64_t B, int64_t Vp, int parts, f
     if (softcap > 0.f) { v = softcap * tanh_f(v / softcap); *p = v; }
     const uint32_t bits = __float_as_uint(v);
     const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-    const unsigned long long q = ((unsigned long long)key << 32) | (uint32_t)g;
+    const unsigned long long q = ((unsigned long long)key << 32) | ((uint32_t)g + idx_off);
     best = q > best ? q : best;
   }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -277,6 +278,95 @@ __global__ void k_argmax_finish(unsigned long long* best, int64_t B, uint32_t* t
     tokens[b] = t;
     if (history) history[b * hist_ld + count] = t;
     best[b] = 0ull;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && advance) {
+    *count_dev = count + 1;
+    *pos_dev += 1;
+  }
+}
+
+// Bounded wait until a flag written by another GPU reaches `want`; on expiry raises the
+// context's error word and gives up (the caller carries on with whatever data is there).
+__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t want, int32_t* err) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v == want) return true;
+    if ((it & 0xFF) == 0xFF) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 1000000000ull) { *err = DEV_TIMEOUT; return false; }
+    }
+  }
+}
+
+// One block per row: x[m, :] += addends of all ranks (rank order), then the row's RMSNorm.
+template <int OUT_BF16>
+__global__ void k_rmsnorm_reduce(PeerPush px, float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t H,
+                                 void* out, int32_t* err) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float sh[32];
+  const uint32_t e = *(volatile uint32_t*)px.epoch;  // the reduction the preceding kernel pushed
+  const uint32_t par = e & 1u;
+  if ((int)threadIdx.x < px.world) wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
+  __syncthreads();
+  const int64_t m = blockIdx.x;
+  float* row = x + m * ldx;
+  const float* slots = px.data[px.rank] + (int64_t)par * px.world * px.max_elems + m * H;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+    float acc = row[i];
+    for (int r = 0; r < px.world; ++r) acc += __ldcg(slots + (int64_t)r * px.max_elems + i);
+    row[i] = acc;
+    ss += acc * acc;
+  }
+  ss = block_sum(ss, sh);
+  const float rms = sqrtf(ss / (float)H + eps);
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+    const float g = plus_one ? 1.f + gamma[i] : gamma[i];
+    const float v = row[i] / rms * g;  // this thread's own store above
+    if (OUT_BF16) ((__nv_bfloat16*)out)[m * H + i] = __float2bfloat16_rn(v);
+    else ((float*)out)[m * H + i] = v;
+  }
+}
+
+// One block: push this rank's per-row candidates, collect every rank's, publish the tokens.
+__global__ void k_argmax_finish_tp(PeerPush px, unsigned long long* best, int64_t B, uint32_t* tokens, uint32_t* history,
+                                   int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance, int32_t* err) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t e = *(volatile uint32_t*)px.epoch + 1u;
+  const uint32_t par = e & 1u;
+  const int64_t mine = ((int64_t)par * px.world + px.rank) * px.max_elems;
+  for (int64_t b = threadIdx.x; b < B; b += blockDim.x) {
+    const unsigned long long v = best[b];
+    best[b] = 0ull;
+    for (int r = 0; r < px.world; ++r) ((unsigned long long*)(px.data[r] + mine))[b] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < px.world; ++r)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(px.flags[r] + par * px.world + px.rank), "r"(e) : "memory");
+    *(volatile uint32_t*)px.epoch = e;
+  }
+  if ((int)threadIdx.x < px.world) wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
+  __syncthreads();
+  const int64_t count = *count_dev;
+  for (int64_t b = threadIdx.x; b < B; b += blockDim.x) {
+    unsigned long long m = 0ull;
+    for (int r = 0; r < px.world; ++r) {
+      const unsigned long long v =
+          __ldcg((const unsigned long long*)(px.data[px.rank] + ((int64_t)par * px.world + r) * px.max_elems) + b);
+      m = v > m ? v : m;
+    }
+    const uint32_t t = (uint32_t)(m & 0xFFFFFFFFull);
+    tokens[b] = t;
+    if (history) history[b * hist_ld + count] = t;
   }
   __syncthreads();
   if (threadIdx.x == 0 && advance) {
@@ -378,10 +468,41 @@ int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, 
   if (B == 0) return CG_OK;
   const int64_t total = (int64_t)parts * Vp;
   const unsigned chunks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(64, total / 1024));
-  CG_CUDA(c, launch_kernel(c, k_argmax_part, dim3(chunks, (unsigned)B), dim3(256), 0, 1, logits, B, Vp, parts, softcap, best));
+  CG_CUDA(c, launch_kernel(c, k_argmax_part, dim3(chunks, (unsigned)B), dim3(256), 0, 1, logits, B, Vp, parts, softcap, best,
+                           (uint32_t)0));
   CG_LAUNCHED(c);
   CG_CUDA(c, launch_kernel(c, k_argmax_finish, dim3(1), dim3(64), 0, 1, best, B, tokens, history, hist_ld, count_dev, pos_dev,
                            advance));
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rmsnorm_reduce(cg_ctx* c, const PeerPush& px, float* x, int64_t ldx, const float* gamma, float eps, int plus_one,
+                            int64_t M, int64_t H, void* out, int out_bf16) {
+  if (M == 0) return CG_OK;
+  if (M * H > px.max_elems) return fail(c, CG_ERR_INVALID, "rmsnorm_reduce: rows do not fit the exchange area");
+  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (out_bf16)
+    CG_CUDA(c, launch_kernel(c, k_rmsnorm_reduce<1>, dim3((unsigned)M), dim3(block), 0, 1, px, x, ldx, gamma, eps, plus_one, H, out,
+                             c->core->dev_err));
+  else
+    CG_CUDA(c, launch_kernel(c, k_rmsnorm_reduce<0>, dim3((unsigned)M), dim3(block), 0, 1, px, x, ldx, gamma, eps, plus_one, H, out,
+                             c->core->dev_err));
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_argmax_tp(cg_ctx* c, const PeerPush& px, float* logits, int64_t B, int64_t Vp, float softcap, uint32_t* tokens,
+                       uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
+                       unsigned long long* best) {
+  if (B == 0) return CG_OK;
+  if (2 * B > px.max_elems) return fail(c, CG_ERR_INVALID, "argmax: rows do not fit the exchange area");
+  const unsigned chunks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(64, Vp / 1024));
+  CG_CUDA(c, launch_kernel(c, k_argmax_part, dim3(chunks, (unsigned)B), dim3(256), 0, 1, logits, B, Vp, 1, softcap, best,
+                           (uint32_t)((int64_t)px.rank * Vp)));
+  CG_LAUNCHED(c);
+  CG_CUDA(c, launch_kernel(c, k_argmax_finish_tp, dim3(1), dim3(64), 0, 1, px, best, B, tokens, history, hist_ld, count_dev, pos_dev,
+                           advance, c->core->dev_err));
   CG_LAUNCHED(c);
   return CG_OK;
 }

@@ -40,6 +40,8 @@ struct DecArgs {
   int kb_total, kb_per_split, splits, stages;
   int32_t* err;
   int trace;  // slot in the timeline buffer, or -1
+  PeerPush push;  // out_mode 3
+  int total_ctas;
 };
 
 // Timeline of the decode GEMM launches (diagnostics): per slot {first CTA start, predecessor
@@ -54,10 +56,16 @@ __device__ __forceinline__ void trace_max(int slot, int f) {
   if (slot >= 0) atomicMax(&g_trace[slot * 4 + f], (unsigned long long)globaltimer());
 }
 
-__device__ __forceinline__ void finish(const DecArgs& p, int m, int n, float g, float u) {
+__device__ __forceinline__ void finish(const DecArgs& p, int m, int n, float g, float u, uint32_t parity) {
   float v = g;
   if (p.dual) v = (p.act == 0 ? silu_f(g) : gelu_f(g)) * u;
   const int64_t o = (int64_t)m * p.ldo + n;
+  if (p.out_mode == 3) {
+    // this rank's addend goes into slot [parity][rank] of every rank's exchange area
+    const int64_t slot = ((int64_t)parity * p.push.world + p.push.rank) * p.push.max_elems + o;
+    for (int r = 0; r < p.push.world; ++r) p.push.data[r][slot] = v;
+    return;
+  }
   if (p.out_mode == 0) ((float*)p.out)[o] = v;
   else if (p.out_mode == 1) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
   else ((float*)p.out)[o] = v + p.residual[o];
@@ -174,6 +182,10 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   }
 
   const bool cluster = p.splits > 1;
+  // the reduction this kernel contributes to: one more than the last one this rank pushed
+  // (stable until this kernel's last CTA has seen every other CTA finish)
+  uint32_t parity = 0;
+  if (p.out_mode == 3 && warp >= 2) parity = (*(volatile uint32_t*)p.push.epoch + 1u) & 1u;
   if (warp >= 2 && acc_ok) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -196,7 +208,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j >= p.M) break;
-          finish(p, c0 + j, n, __uint_as_float(g[j]), p.dual ? __uint_as_float(u[j]) : 0.f);
+          finish(p, c0 + j, n, __uint_as_float(g[j]), p.dual ? __uint_as_float(u[j]) : 0.f, parity);
         }
       }
     }
@@ -218,7 +230,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
           if (p.dual) u += ld_cluster_f32(base + (uint32_t)((TN + col) * BM + row) * 4u, (uint32_t)s);
         }
         const int n = n0 + row;
-        if (n < p.N) finish(p, col, n, g, u);
+        if (n < p.N) finish(p, col, n, g, u, parity);
       }
     }
     __syncwarp();
@@ -230,6 +242,21 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   if (warp == 1) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
+  }
+  if (p.out_mode == 3 && tid == 0) {
+    // every thread's pushes precede the barrier above; the fence orders them (system wide)
+    // before this CTA's ticket, and the CTA that draws the last ticket raises the flags
+    __threadfence_system();
+    const unsigned t = atomicAdd(p.push.ticket, 1u);
+    if (t == (unsigned)p.total_ctas - 1u) {
+      *p.push.ticket = 0u;
+      const uint32_t e = *(volatile uint32_t*)p.push.epoch + 1u;
+      __threadfence_system();
+      for (int r = 0; r < p.push.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push.flags[r] + (e & 1u) * p.push.world + p.push.rank), "r"(e)
+                     : "memory");
+      *(volatile uint32_t*)p.push.epoch = e;
+    }
   }
   if (tid == 0) trace_max(p.trace, 3);
 }
@@ -289,6 +316,14 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   a.kb_total = kb_total; a.kb_per_split = kb_per; a.splits = splits; a.stages = stages;
   a.err = c->core->dev_err;
   a.trace = c->trace_on ? (int)(c->trace_next++ % TRACE_SLOTS) : -1;
+  a.total_ctas = (int)(tiles * splits);
+  if (g.out_mode == 3) {
+    if (!g.push || g.dual || g.M * g.ldo > g.push->max_elems)
+      return fail(c, CG_ERR_INVALID, "gemm_dec: the pushed addend does not fit the exchange area");
+    a.push = *g.push;
+  } else {
+    a.push = PeerPush{};
+  }
   dim3 grid((unsigned)tiles, 1, (unsigned)splits);
   if (tn == 16) return launch_dec<16>(c, mw, mx, a, grid, smem);
   return launch_dec<32>(c, mw, mx, a, grid, smem);

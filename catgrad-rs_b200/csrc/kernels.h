@@ -94,6 +94,34 @@ int k_launch_argmax(cg_ctx* c, float* logits, int64_t B, int64_t Vp, int parts, 
                     uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
                     unsigned long long* best);
 
+// What a kernel needs to push an addend of a small all-reduce into every rank's exchange
+// area (see PeerXchg) and what the consumer needs to collect it.
+struct PeerPush {
+  float* data[MAX_PEERS];
+  uint32_t* flags[MAX_PEERS];
+  uint32_t* epoch;
+  unsigned* ticket;
+  int world, rank;
+  int64_t max_elems;
+};
+inline PeerPush peer_push_of(const PeerXchg& x) {
+  PeerPush p;
+  for (int r = 0; r < MAX_PEERS; ++r) { p.data[r] = x.data[r]; p.flags[r] = x.flags[r]; }
+  p.epoch = x.epoch; p.ticket = x.ticket; p.world = x.world; p.rank = x.rank; p.max_elems = x.max_elems;
+  return p;
+}
+
+// x[m, :] += sum over ranks (in rank order) of the addends pushed for the latest reduction,
+// then out = rmsnorm(x) as k_launch_rmsnorm.  Waits (bounded) for every rank's flag first.
+int k_launch_rmsnorm_reduce(cg_ctx* c, const PeerPush& px, float* x, int64_t ldx, const float* gamma, float eps, int plus_one,
+                            int64_t M, int64_t H, void* out, int out_bf16);
+// Tensor-parallel greedy pick: every rank reduces its own vocabulary slice [B, Vp] (global
+// index = rank * Vp + i) to one candidate per row, pushes the candidates to all ranks, and
+// every rank takes the best (ties -> last index) and advances its counters as k_launch_argmax.
+int k_launch_argmax_tp(cg_ctx* c, const PeerPush& px, float* logits, int64_t B, int64_t Vp, float softcap, uint32_t* tokens,
+                       uint32_t* history, int64_t hist_ld, int64_t* count_dev, int64_t* pos_dev, int advance,
+                       unsigned long long* best);
+
 // Weight-streaming GEMM for a handful of tokens (M <= 32): y[M, N] = x[M, K] w[N, K]^T on bf16
 // activations.  The gate/up pair can share a CTA with act(gate) * up as the epilogue, and
 // split-K partials are reduced inside a thread-block cluster.
@@ -105,7 +133,9 @@ struct DecGemm {
   void* out;                // [M, N] with row stride ldo
   int64_t ldo;
   const float* residual;
-  int out_mode;             // 0: f32, 1: bf16, 2: f32 out = product + residual
+  int out_mode;             // 0: f32, 1: bf16, 2: f32 out = product + residual,
+                            // 3: the product is pushed as this rank's addend of an all-reduce (out unused)
+  const PeerPush* push;     // for out_mode 3
   int dual;                 // 1: rows n and n + N of w form gate and up; out = act(gate) * up
   int act;                  // 0 silu, 1 tanh-gelu
   int64_t M, N, K;

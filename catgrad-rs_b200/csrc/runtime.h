@@ -53,6 +53,26 @@ struct Core {
   void trim();
 };
 
+// Peer exchange area for small all-reduces without a library call: every rank owns
+// data[2][world][max_elems] f32 and flags[2][world] u32 in its own memory and maps the areas
+// of all ranks.  A rank pushes its addend into slot [parity][its rank] of EVERY rank's area,
+// then raises that slot's flag to the reduction's sequence number; a consumer waits for the
+// `world` flags of its own area and sums the slots in rank order.  Two parities alternate so
+// a fast rank's next push cannot overwrite what a slow rank still reads.
+constexpr int MAX_PEERS = 8;
+struct PeerXchg {
+  bool ok = false;
+  int world = 1, rank = 0;
+  int64_t max_elems = 0;               // floats per slot
+  float* data[MAX_PEERS] = {nullptr};  // base of every rank's data area (index = rank; own = local)
+  uint32_t* flags[MAX_PEERS] = {nullptr};
+  uint32_t* epoch = nullptr;           // local: sequence number of the last reduction this rank pushed
+  unsigned* ticket = nullptr;          // local: CTAs of the pushing kernel that are done
+  void* local_base = nullptr;
+  void* opened[MAX_PEERS] = {nullptr};
+  std::string why;                     // when !ok: what failed during set-up
+};
+
 }  // namespace cg
 
 struct cg_ctx {
@@ -62,10 +82,12 @@ struct cg_ctx {
   int64_t launches = 0;
   int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
   int opt_pdl = 1;        // programmatic dependent launch for the fused kernels
+  int opt_peer = 1;       // small all-reduces over mapped peer memory instead of NCCL (when available)
   bool trace_on = false;  // record a device timeline of the decode GEMM launches
   int64_t trace_next = 0;
   void* comm = nullptr;   // ncclComm_t
   int comm_rank = 0, comm_world = 1;
+  cg::PeerXchg xchg;
   // host function pointer of cuTensorMapEncodeTiled, resolved on first use
   void* encode_tiled = nullptr;
 };

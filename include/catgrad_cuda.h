@@ -160,6 +160,10 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
 /* Runtime switches (name, value):
  *   "gemm"  : 0 = auto (tcgen05 bf16 when an operand is stored bf16, else f32 SIMT),
  *             1 = force the f32 SIMT kernel (cross-check path for tests)
+ *   "pdl"   : 1 (default) = fused kernels are launched with programmatic stream serialization
+ *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
+ *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
+ *             decode step, and identically on every rank.
  */
 int32_t cg_set_option(cg_ctx*, const char* name, int64_t value);
 
@@ -315,8 +319,15 @@ int32_t cg_argmax_rows_noalloc(void* stream, const float* logits, int64_t rows, 
 /* Size in bytes of the opaque id rank 0 creates and every rank must receive. */
 int32_t cg_comm_id_size(void);
 int32_t cg_comm_make_id(void* id_bytes);
-/* Collective: every rank calls with the same id. */
+/* Collective: every rank calls with the same id.  Besides the NCCL communicator this maps a
+ * small exchange area of every rank into every other rank (CUDA inter-process handles,
+ * carried by the new communicator), used by the decoder for reductions of a few tokens:
+ * the row-parallel GEMM writes its partial product straight into all ranks' areas and the
+ * norm kernel that follows sums them, so a decode step makes no collective call. */
 int32_t cg_comm_init(cg_ctx*, const void* id_bytes, int32_t rank, int32_t world);
+/* 1 when the peer exchange area is mapped on this rank (and therefore on all), else 0 with
+ * the reason in `why` (the decoder then keeps to NCCL collectives). */
+int32_t cg_comm_peer_exchange(cg_ctx*, char* why, int64_t why_cap);
 int32_t cg_comm_destroy(cg_ctx*);
 /* In-place sum all-reduce of an F32-tagged contiguous tensor (f32 or bf16 storage). */
 int32_t cg_comm_all_reduce(cg_ctx*, cg_tensor* t);

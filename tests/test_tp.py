@@ -95,14 +95,22 @@ GPU_WORKER = textwrap.dedent("""
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     C = cg.CudaBackend(local, cg.PREC_BF16)
     cg.tp.init_comm(C, rank, world)
+    C.set_option("peer", {peer})
     cfg = cg.synth.ModelConfig("tp-gpu", 256, 512, 2, 4, 2, 1024, rope_theta=500000.0, tie_word_embeddings=True, dtype="bf16")
     prompt = cg.synth.make_tokens(cfg, 3, 40, seed=2)
     dec = cg.Decoder(C, cfg, max_seq=64, max_batch=3, tp_rank=rank, tp_world=world)
     dec.load(cg.synth.make_weights(cfg, 0))
     lg = C.to_numpy(dec.prefill(C.from_numpy(prompt), want_logits=True))
     toks = dec.generate(prompt, 10)
+    # decode-step logits (gathered on demand): force the same tokens on every configuration
+    dec.prefill(C.from_numpy(prompt))
+    forced = np.uint32([[7, 8, 9], [100, 200, 300], [5, 5, 5]])
+    step_lg = [C.to_numpy(dec.step_with(C.from_numpy(forced[i]), want_logits=True)) for i in range(3)]
+    mapped, why = C.peer_exchange()
+    if {want_peer!r} and not mapped:
+        raise SystemExit("peer exchange not mapped: " + why)
     if rank == 0:
-        np.save({out!r}, np.concatenate([lg.ravel(), toks.ravel().astype(np.float32)]))
+        np.save({out!r}, np.concatenate([lg.ravel(), toks.ravel().astype(np.float32)] + [a.ravel() for a in step_lg]))
     dec.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -110,13 +118,16 @@ GPU_WORKER = textwrap.dedent("""
 
 
 @pytest.mark.gpu
-def test_tensor_parallel_decoder_matches_one_gpu(tmp_path):
+@pytest.mark.parametrize("peer", [1, 0], ids=["peer-push", "nccl"])
+def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer):
+    """peer=1: decode steps reduce over mapped peer memory (GEMM epilogue pushes, norm kernel
+    sums); peer=0: NCCL all-reduce / all-gather.  Both must reproduce one GPU."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "tp.npy")
     script = tmp_path / "tp_gpu_worker.py"
-    script.write_text(GPU_WORKER.format(root=ROOT, out=out))
+    script.write_text(GPU_WORKER.format(root=ROOT, out=out, peer=peer, want_peer=bool(peer)))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29612", str(script)],
@@ -130,7 +141,11 @@ def test_tensor_parallel_decoder_matches_one_gpu(tmp_path):
     dec.load(cg.synth.make_weights(cfg, 0))
     lg = C.to_numpy(dec.prefill(C.from_numpy(prompt), want_logits=True))
     toks = dec.generate(prompt, 10)
+    dec.prefill(C.from_numpy(prompt))
+    forced = np.uint32([[7, 8, 9], [100, 200, 300], [5, 5, 5]])
+    step_lg = np.concatenate([C.to_numpy(dec.step_with(C.from_numpy(forced[i]), want_logits=True)).ravel() for i in range(3)])
     n = lg.size
     np.testing.assert_allclose(got[:n].reshape(lg.shape), lg, rtol=0, atol=2e-2)
-    same = (got[n:].reshape(toks.shape).astype(np.uint32) == toks).mean()
+    same = (got[n:n + toks.size].reshape(toks.shape).astype(np.uint32) == toks).mean()
     assert same >= 0.8, same  # summation order differs across ranks; near-ties may flip a token
+    np.testing.assert_allclose(got[n + toks.size:], step_lg, rtol=0, atol=2e-2)
