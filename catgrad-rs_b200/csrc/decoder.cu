@@ -39,7 +39,7 @@ struct Layer {
   cg_tensor *k_cache = nullptr, *v_cache = nullptr;
   // mixture-of-experts layers (qwen3.rs:64-133): router [E, H] f32, this rank's experts stacked
   bool moe = false;
-  cg_tensor *router = nullptr, *we_gate = nullptr, *we_up = nullptr, *we_down = nullptr;
+  cg_tensor *router = nullptr, *router3 = nullptr, *we_gate = nullptr, *we_up = nullptr, *we_down = nullptr;
 };
 
 void drop(cg_tensor*& t) {
@@ -71,7 +71,7 @@ struct cg_decoder {
             *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *best = nullptr;
   // mixture-of-experts scratch, sized for cap * top_k pairs
   cg_tensor *m_ids = nullptr, *m_wts = nullptr, *m_pos = nullptr, *m_tiles = nullptr, *m_xg = nullptr, *m_h = nullptr,
-            *m_y = nullptr;
+            *m_y = nullptr, *m_xs3 = nullptr, *m_logits = nullptr;
   int El = 0;                    // experts on this rank
   int attn_splits = 1;
   bool pending_reduce = false;   // x still lacks the addends pushed by the last row-parallel GEMM
@@ -146,6 +146,11 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->hact));
   if (D->cfg.n_experts > 0) {
     drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
+    drop(D->m_xs3); drop(D->m_logits);
+    s2[0] = M; s2[1] = 3 * H;
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->m_xs3));
+    s2[1] = D->cfg.n_experts;
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->m_logits));
     const int64_t P = M * D->cfg.top_k;
     int64_t n = P;
     CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->m_ids));
@@ -178,6 +183,9 @@ int moe_block(cg_decoder* D, Layer& L, int64_t M) {
   a.eps = cfg.rms_eps;
   a.plus_one = cfg.norm_plus_one;
   a.router = (const float*)L.router->data();
+  a.router3 = (const __nv_bfloat16*)L.router3->data();
+  a.xs3 = (__nv_bfloat16*)D->m_xs3->data();
+  a.logits = (float*)D->m_logits->data();
   a.w_gate = (const __nv_bfloat16*)L.we_gate->data();
   a.w_up = (const __nv_bfloat16*)L.we_up->data();
   a.w_down = (const __nv_bfloat16*)L.we_down->data();
@@ -485,13 +493,14 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
     drop(L.w_qkv); drop(L.w_o); drop(L.w_gu); drop(L.w_down); drop(L.ln_in); drop(L.ln_post_attn);
     if (L.ln_pre_ffn) drop(L.ln_pre_ffn);
     drop(L.ln_post_ffn); drop(L.q_norm); drop(L.k_norm); drop(L.k_cache); drop(L.v_cache);
-    drop(L.router); drop(L.we_gate); drop(L.we_up); drop(L.we_down);
+    drop(L.router); drop(L.router3); drop(L.we_gate); drop(L.we_up); drop(L.we_down);
   }
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
   drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best);
   drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
+  drop(D->m_xs3); drop(D->m_logits);
   delete D;
   return CG_OK;
 }
@@ -537,6 +546,17 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
           ed->dims[0] != E || ed->dims[1] != H || ed->dims[2] != Fe)
         return fail(c, CG_ERR_SHAPE, "decoder: expert parameters have unexpected shapes");
       CG_TRY(as_contiguous_f32(c, wr, &L.router));
+      {
+        // the router matrix three times along k, for the split-precision router GEMM
+        Hold rb;
+        CG_TRY(cg_to_bf16(c, wr, &rb.t));
+        int64_t r3[2] = {E, 3 * H};
+        CG_TRY(new_tensor(c, CG_F32, ST_BF16, r3, 2, &L.router3));
+        for (int rep3 = 0; rep3 < 3; ++rep3)
+          CG_CUDA(c, cudaMemcpy2DAsync((__nv_bfloat16*)L.router3->data() + rep3 * H, (size_t)3 * H * 2, rb.t->data(), (size_t)H * 2,
+                                       (size_t)H * 2, (size_t)E, cudaMemcpyDeviceToDevice, c->core->stream));
+        CG_CUDA(c, cudaStreamSynchronize(c->core->stream));  // rb is released at the end of this scope
+      }
       for (auto pr : {std::make_pair(eg, &L.we_gate), std::make_pair(eu, &L.we_up), std::make_pair(ed, &L.we_down)}) {
         cg_tensor* sl = nullptr;
         CG_TRY(cg_slice(c, pr.first, 0, (int64_t)R * El, El, &sl));

@@ -160,7 +160,10 @@ struct MoeArgs {
   const float* gamma;         // norm weights [H]; null = x is used as it is
   float eps;
   int plus_one;
-  const float* router;        // [E, H] f32
+  const float* router;        // [E, H] f32 (used when router3 is null)
+  const __nv_bfloat16* router3;  // [E, 3 H] bf16: the router matrix three times along k, or null
+  __nv_bfloat16* xs3;         // [M, 3 H] scratch for router3
+  float* logits;              // [M, E] scratch for router3
   const __nv_bfloat16 *w_gate, *w_up;  // [El, Fe, H] experts this rank owns
   const __nv_bfloat16* w_down;         // [El, H, Fe]
   int H, E, k, Fe, norm_topk, act;

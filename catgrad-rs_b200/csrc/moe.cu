@@ -118,9 +118,96 @@ __global__ void k_moe_route(const float* x, const float* gamma, float eps, int p
   }
 }
 
-// One block.  Counts the pairs routed to experts [e_lo, e_lo + El), lays the groups out back
-// to back, lists the GEMM tiles (tn rows each, never crossing a group) and gives every pair
-// its row (or -1 when another rank owns its expert).
+// Router on the tensor cores without giving up f32 routing: the normalised row v is written
+// three times in bf16 -- hi = bf16(v), lo = bf16(v - hi), lo2 = bf16(v - hi - lo), which sum to
+// v to within an ulp of f32 -- and multiplied with the (bf16) router matrix repeated three
+// times along k.  Every product is exact in f32, only the accumulation order differs from
+// the reference's.  One block per token; also writes the plain bf16 row the experts read.
+__global__ void k_moe_norm_split(const float* x, const float* gamma, float eps, int plus_one, int H, __nv_bfloat16* xn,
+                                 __nv_bfloat16* xs3) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float red[32];
+  const int64_t m = blockIdx.x;
+  const float* row = x + m * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ss += row[i] * row[i];
+  ss = block_sum_f(ss, red);
+  const float rms = sqrtf(ss / (float)H + eps);
+  __nv_bfloat16* o3 = xs3 + m * 3 * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = gamma ? row[i] / rms * (plus_one ? 1.f + gamma[i] : gamma[i]) : row[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo2 = __float2bfloat16_rn(r1 - __bfloat162float(lo));
+    xn[m * H + i] = hi;
+    o3[i] = hi;
+    o3[H + i] = lo;
+    o3[2 * H + i] = lo2;
+  }
+}
+
+// One warp per token: softmax over the router logits, top-k (ties -> lower expert id),
+// optional renormalisation.  Dynamic shared memory: E floats per warp.
+__global__ void k_moe_topk(const float* logits, int64_t M, int E, int k, int norm_topk, uint32_t* ids, float* wts) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int64_t m = (int64_t)blockIdx.x * nw + wid;
+  if (m >= M) return;
+  float* pr = sm + (size_t)wid * E;
+  const float* lg = logits + m * E;
+  float mx = -3.4028234663852886e38f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = lg[e];
+    pr[e] = v;
+    mx = fmaxf(mx, v);
+  }
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(pr[e] - mx);
+    pr[e] = v;
+    sum += v;
+  }
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) pr[e] = pr[e] / sum;
+  __syncwarp();
+  float chosen = 0.f, total = 0.f;
+  uint32_t chosen_id = 0;
+  for (int r = 0; r < k; ++r) {
+    unsigned long long best = 0;
+    for (int e = lane; e < E; e += 32) {
+      const float v = pr[e];
+      if (v < 0.f) continue;
+      const unsigned long long q = ((unsigned long long)__float_as_uint(v) << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)e);
+      best = q > best ? q : best;
+    }
+    for (int o = 16; o; o >>= 1) {
+      const unsigned long long w = __shfl_xor_sync(0xffffffffu, best, o);
+      best = w > best ? w : best;
+    }
+    const uint32_t e = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
+    const float v = __uint_as_float((uint32_t)(best >> 32));
+    total += v;
+    if (lane == r) { chosen = v; chosen_id = e; }
+    if (lane == 0) pr[e] = -1.f;
+    __syncwarp();
+  }
+  if (lane < k) {
+    ids[m * k + lane] = chosen_id;
+    wts[m * k + lane] = norm_topk ? chosen / total : chosen;
+  }
+}
+
+// One block of 1024 threads (El <= 1024).  Counts the pairs routed to experts
+// [e_lo, e_lo + El), lays the groups out back to back, lists the GEMM tiles (tn rows each,
+// never crossing a group) and gives every pair its row (or -1 when another rank owns its
+// expert).  Thread e owns expert e: two block-wide prefix sums give its first row and its
+// first tile.
 __global__ void k_moe_plan(const uint32_t* ids, int P, int e_lo, int El, int tn, int32_t* pos, int32_t* tile_expert,
                            int32_t* tile_row0, int32_t* tile_rows, int32_t* n_tiles) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -128,30 +215,47 @@ __global__ void k_moe_plan(const uint32_t* ids, int P, int e_lo, int El, int tn,
   extern __shared__ int sh_i[];
   int* cnt = sh_i;          // [El]
   int* cur = sh_i + El;     // [El]
-  for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
+  __shared__ int wsum_rows[32], wsum_tiles[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  for (int e = tid; e < El; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+  for (int p = tid; p < P; p += blockDim.x) {
     const int e = (int)ids[p] - e_lo;
     if (e >= 0 && e < El) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int off = 0, nt = 0;
-    for (int e = 0; e < El; ++e) {
-      const int n = cnt[e];
-      cur[e] = off;
-      for (int r = 0; r < n; r += tn) {
-        tile_expert[nt] = e;
-        tile_row0[nt] = off + r;
-        tile_rows[nt] = min(tn, n - r);
-        ++nt;
-      }
-      off += n;
+  const int n = tid < El ? cnt[tid] : 0;
+  const int nt = (n + tn - 1) / tn;
+  int rows_incl = n, tiles_incl = nt;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, rows_incl, o), b = __shfl_up_sync(0xffffffffu, tiles_incl, o);
+    if (lane >= o) { rows_incl += a; tiles_incl += b; }
+  }
+  if (lane == 31) { wsum_rows[wid] = rows_incl; wsum_tiles[wid] = tiles_incl; }
+  __syncthreads();
+  if (wid == 0) {
+    int a = wsum_rows[lane], b = wsum_tiles[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a2 = __shfl_up_sync(0xffffffffu, a, o), b2 = __shfl_up_sync(0xffffffffu, b, o);
+      if (lane >= o) { a += a2; b += b2; }
     }
-    *n_tiles = nt;
+    wsum_rows[lane] = a;
+    wsum_tiles[lane] = b;
   }
   __syncthreads();
-  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+  const int row0 = rows_incl - n + (wid ? wsum_rows[wid - 1] : 0);
+  const int tile0 = tiles_incl - nt + (wid ? wsum_tiles[wid - 1] : 0);
+  if (tid < El) {
+    cur[tid] = row0;
+    for (int t = 0; t < nt; ++t) {
+      tile_expert[tile0 + t] = tid;
+      tile_row0[tile0 + t] = row0 + t * tn;
+      tile_rows[tile0 + t] = min(tn, n - t * tn);
+    }
+  }
+  if (tid == blockDim.x - 1) *n_tiles = tile0 + nt;
+  __syncthreads();
+  for (int p = tid; p < P; p += blockDim.x) {
     const int e = (int)ids[p] - e_lo;
     pos[p] = (e >= 0 && e < El) ? atomicAdd(&cur[e], 1) : -1;
   }
@@ -384,14 +488,32 @@ int64_t moe_max_tiles(int64_t pairs, int experts_local, int tn) {
 int moe_ffn(cg_ctx* c, const MoeArgs& a) {
   if (a.M == 0) return CG_OK;
   if (a.k < 1 || a.k > 32 || a.k > a.E) return fail(c, CG_ERR_UNSUPPORTED, "moe: experts per token must be in [1, 32]");
-  if (a.E > 4096 || a.H % 8 || a.Fe % 8) return fail(c, CG_ERR_UNSUPPORTED, "moe: sizes must be multiples of 8, at most 4096 experts");
+  if (a.E > 1024 || a.H % 8 || a.Fe % 8) return fail(c, CG_ERR_UNSUPPORTED, "moe: sizes must be multiples of 8, at most 1024 experts");
   const int64_t P = a.M * a.k;
   if (P > 2147483647ll / 4) return fail(c, CG_ERR_UNSUPPORTED, "moe: too many (token, expert) pairs");
   const int tn = moe_pick_tn(P, a.E);
   const int64_t max_tiles = moe_max_tiles(P, a.El, tn);
   if (max_tiles > 65535) return fail(c, CG_ERR_UNSUPPORTED, "moe: too many tiles");
 
-  {
+  if (a.router3) {
+    CG_CUDA(c, launch_kernel(c, k_moe_norm_split, dim3((unsigned)a.M), dim3(256), 0, 1, a.x, a.gamma, a.eps, a.plus_one, a.H, a.xn,
+                             a.xs3));
+    CG_LAUNCHED(c);
+    const int64_t K3 = 3 * (int64_t)a.H;
+    if (gemm_dec_supported(a.M, K3)) {
+      DecGemm g;
+      g.x = a.xs3; g.ldx = K3; g.w = a.router3; g.ldw = K3; g.w_rows = a.E;
+      g.out = a.logits; g.ldo = a.E; g.residual = nullptr; g.out_mode = 0; g.push = nullptr; g.dual = 0; g.act = 0;
+      g.M = a.M; g.N = a.E; g.K = K3;
+      CG_TRY(gemm_dec(c, g));
+    } else {
+      CG_TRY(gemm_tc(c, a.xs3, K3, a.router3, K3, a.logits, a.E, nullptr, a.M, a.E, K3, 0, 0, nullptr));
+    }
+    const int warps = 4;
+    CG_CUDA(c, launch_kernel(c, k_moe_topk, dim3((unsigned)((a.M + warps - 1) / warps)), dim3(32 * warps),
+                             (size_t)warps * a.E * 4, 1, (const float*)a.logits, a.M, a.E, a.k, a.norm_topk, a.w.ids, a.w.wts));
+    CG_LAUNCHED(c);
+  } else {
     const size_t smem = (size_t)(a.H + a.E) * 4;
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -465,7 +587,7 @@ extern "C" int32_t cg_fused_moe(cg_ctx* c, const cg_tensor* x, const cg_tensor* 
     return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
   if (act != 0 && act != 1) return fail(c, CG_ERR_INVALID, "unknown activation");
   if (top_k < 1 || top_k > E) return fail(c, CG_ERR_SHAPE, "moe: top_k out of range");
-  Hold xc, rc, gb, ub, db, r, ids, wts, pos, tiles, xn, xg, h, y;
+  Hold xc, rc, gb, ub, db, r, ids, wts, pos, tiles, xn, xg, h, y, r3, xs3, lgt;
   CG_TRY(as_contiguous_f32(c, x, &xc.t));
   CG_TRY(as_contiguous_f32(c, router, &rc.t));
   for (auto pr : {std::make_pair(gate, &gb), std::make_pair(up, &ub), std::make_pair(down, &db)}) {
@@ -495,6 +617,24 @@ extern "C" int32_t cg_fused_moe(cg_ctx* c, const cg_tensor* x, const cg_tensor* 
     a.out = (float*)r.t->data();
     a.gamma = nullptr; a.eps = 0.f; a.plus_one = 0;
     a.router = (const float*)rc.t->data();
+    a.router3 = nullptr; a.xs3 = nullptr; a.logits = nullptr;
+    if (router->storage == ST_BF16) {
+      // bf16 router weights: the split-precision tensor-core router
+      Hold rb;
+      CG_TRY(cg_to_bf16(c, router, &rb.t));
+      int64_t d3[2] = {E, 3 * H};
+      CG_TRY(new_tensor(c, CG_F32, ST_BF16, d3, 2, &r3.t));
+      for (int rep3 = 0; rep3 < 3; ++rep3)
+        CG_CUDA(c, cudaMemcpy2DAsync((__nv_bfloat16*)r3.t->data() + rep3 * H, (size_t)3 * H * 2, rb.t->data(), (size_t)H * 2,
+                                     (size_t)H * 2, (size_t)E, cudaMemcpyDeviceToDevice, c->core->stream));
+      d3[0] = M;
+      CG_TRY(new_tensor(c, CG_F32, ST_BF16, d3, 2, &xs3.t));
+      d3[1] = E;
+      CG_TRY(new_tensor(c, CG_F32, ST_F32, d3, 2, &lgt.t));
+      a.router3 = (const __nv_bfloat16*)r3.t->data();
+      a.xs3 = (__nv_bfloat16*)xs3.t->data();
+      a.logits = (float*)lgt.t->data();
+    }
     a.w_gate = (const __nv_bfloat16*)gb.t->data();
     a.w_up = (const __nv_bfloat16*)ub.t->data();
     a.w_down = (const __nv_bfloat16*)db.t->data();

@@ -62,6 +62,25 @@ def test_fused_moe_matches_op_stream(oracle, cuda_bf16, S, H, E, Fe, k, renorm):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("S,H,E,Fe,k,renorm", [CASES[1], CASES[5]])
+def test_fused_moe_f32_router(oracle, cuda, S, H, E, Fe, k, renorm):
+    """On an f32-precision context the router matrix stays f32 and the per-token f32 router
+    kernel runs instead of the split-precision tensor-core router."""
+    C = cuda
+    w = moe_case(S * 11 + E, S, H, E, Fe)
+    cfg = synth.ModelConfig("moe-unit", H, 2 * H, 1, 2, 2, 64, head_dim=64, arch="qwen3", num_local_experts=E,
+                            num_experts_per_tok=k, moe_intermediate_size=Fe, norm_topk_prob=renorm)
+    po = {n: oracle.from_numpy(a) for n, a in w.items() if n != "x"}
+    want, want_ids = graphs.qwen3.moe(oracle, cfg, po, "m", oracle.from_numpy(w["x"]))
+    up = lambda n: C.from_numpy(w[n])
+    got, ids = C.fused_moe(C.from_numpy(w["x"].reshape(S, H)), up("m.gate.weight"), up("m.experts.gate_proj.weight"),
+                           up("m.experts.up_proj.weight"), up("m.experts.down_proj.weight"), k, renorm, 0)
+    assert (C.to_numpy(ids) == oracle.to_numpy(want_ids).reshape(S, k)).all()
+    want = oracle.to_numpy(want).reshape(S, H)
+    assert np.abs(C.to_numpy(got) - want).max() <= 1e-2 * float(np.abs(want).max()) + 1e-6
+
+
+@pytest.mark.gpu
 def test_fused_moe_ties_and_errors(cuda_bf16):
     C = cuda_bf16
     S, H, E, Fe = 3, 64, 8, 32
