@@ -338,6 +338,7 @@ int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bflo
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
     return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: k and leading dimensions must be multiples of 8, bases 16-byte aligned");
   if (M > 2147483647ll / 2 || F > 2147483647ll / 4) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: problem too large");
+  if (c->opt_persistent && gemm_tcp_wanted(M, F, K)) return gemm_tcp(c, x, ldx, w, ldw, 2 * F, out, ldo, nullptr, M, F, K, 1, 1, act);
   const int tn = M <= 128 ? 128 : 256;
   CUtensorMap mw, mx;
   CG_TRY(make_map(c, &mw, w, 2 * F, K, ldw, BM));
@@ -361,6 +362,8 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
     return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: k and leading dimensions must be multiples of 8, bases 16-byte aligned");
   if (M > 2147483647ll / 2 || N > 2147483647ll / 2) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: problem too large");
+  if (c->opt_persistent && splits <= 1 && gemm_tcp_wanted(M, N, K))
+    return gemm_tcp(c, x, ldx, w, ldw, N, out, ldo, residual, M, N, K, out_mode, 0, 0);
   const int tn = pick_tn(M);
   const int kb_total = (int)((K + BK - 1) / BK);
   if (splits <= 0) splits = gemm_tc_pick_splits(M, N, K);

@@ -82,6 +82,7 @@ struct cg_ctx {
   int64_t launches = 0;
   int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
   int opt_pdl = 1;        // programmatic dependent launch for the fused kernels
+  int opt_persistent = 1; // large GEMMs take the persistent double-buffered kernel
   int opt_peer = 1;       // small all-reduces over mapped peer memory instead of NCCL (when available)
   bool trace_on = false;  // record a device timeline of the decode GEMM launches
   int64_t trace_next = 0;
@@ -224,6 +225,14 @@ inline int grid_for(int64_t n, int block, int max_blocks = 148 * 16) {
 int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,
             void* out, int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K,
             int out_mode, int splits, float* workspace);
+// Persistent variant for many tokens (double-buffered TMEM accumulators, epilogue overlapped
+// with the next tile's MMAs).  pair != 0: w holds N gate rows then N up rows (w_rows = 2 N) and
+// out[M, N] (bf16) = act(x gate^T) * (x up^T).  gemm_tc and gemm_tc_pair route here by themselves
+// when gemm_tcp_wanted says the problem is large enough.
+bool gemm_tcp_wanted(int64_t M, int64_t N, int64_t K);
+int gemm_tcp(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, int64_t w_rows,
+             void* out, int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K, int out_mode,
+             int pair, int act);
 // Gate and up projections with the activation fused: w holds the gate rows then the up rows
 // ([2 F, K]); out[M, F] (bf16) = act(x gate^T) * (x up^T), act 0 = silu, 1 = tanh-gelu.
 int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,

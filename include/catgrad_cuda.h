@@ -161,6 +161,8 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "gemm"  : 0 = auto (tcgen05 bf16 when an operand is stored bf16, else f32 SIMT),
  *             1 = force the f32 SIMT kernel (cross-check path for tests)
  *   "pdl"   : 1 (default) = fused kernels are launched with programmatic stream serialization
+ *   "persistent" : 1 (default) = GEMMs with several output tiles per SM run as one resident
+ *             CTA per SM with double-buffered accumulators; 0 = one CTA per tile
  *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
  *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
  *             decode step, and identically on every rank.

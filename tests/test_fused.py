@@ -89,7 +89,9 @@ def test_eager_stream_matches_fused_on_device(cuda):
 GEMM_SHAPES = [(1, 128, 64), (8, 256, 2048), (5, 3072, 2048), (16, 200, 72), (17, 136, 128), (33, 128, 4096),
                (100, 384, 512), (130, 256, 192), (300, 1024, 320), (512, 640, 1024),
                # enough tiles for the 256-row two-accumulator variant (token tiles of 256 and of 128), ragged edges
-               (1024, 10240, 128), (1100, 7700, 128), (128, 38000, 64)]
+               (1024, 10240, 128), (1100, 7700, 128), (128, 38000, 64),
+               # several tiles per SM: the persistent kernel with double-buffered accumulators
+               (1024, 9600, 320), (1300, 7700, 264)]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
