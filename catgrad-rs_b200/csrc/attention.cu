@@ -7,8 +7,11 @@
 // order repeat_kv produces.  Masked scores are dropped, which equals adding f32::MIN before
 // the softmax (exp underflows to 0).
 //
-// 64-query x 64-key tiles, bf16 mma.sync with f32 accumulation, 4 warps.  (The one-token
-// decode step has its own fused kernel.)
+// BQ-query x 64-key tiles (BQ = 128 with 8 warps for head sizes up to 128, 64 with 4 warps
+// for 256), bf16 mma.sync with f32 accumulation.  Key/value tiles arrive by cp.async into two
+// shared-memory buffers, so the loads of tile i+1 overlap the math of tile i; query tiles are
+// scheduled longest first (under the causal mask the last tile of a row has the most keys).
+// (The one-token decode step has its own fused kernel.)
 #include "kernels.h"
 #include "mma.cuh"
 
@@ -21,18 +24,18 @@ namespace {
 __device__ __forceinline__ float tanh_sig(float x) { return 2.f / (1.f + __expf(-2.f * x)) - 1.f; }
 
 // ------------------------------------------------------------------ prefill ----------
-template <int D>
-__global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
+template <int D, int BQ, int NBUF>
+__global__ void __launch_bounds__(BQ * 2, D <= 64 ? 2 : 1) k_attn_prefill(AttnArgs a, float scale) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  constexpr int BQ = 64, BKV = 64, LD = D + 8;  // padded rows: conflict-free ldmatrix
+  constexpr int BKV = 64, LD = D + 8, NT = BQ * 2;  // padded rows: conflict-free ldmatrix
   extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* sq = (__nv_bfloat16*)smem;
-  __nv_bfloat16* sk = sq + BQ * LD;
-  __nv_bfloat16* sv = sk + BKV * LD;
+  __nv_bfloat16* sk = sq + BQ * LD;          // [NBUF][BKV][LD]
+  __nv_bfloat16* sv = sk + NBUF * BKV * LD;  // [NBUF][BKV][LD]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = blockIdx.x, h = blockIdx.y;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
   const int64_t b = blockIdx.z;
   const int kvh = h / (a.nh / a.nkv);
   const int64_t q0 = (int64_t)qt * BQ;
@@ -42,7 +45,7 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
 
   // Q tile -> shared (rows past S are zero)
   constexpr int CH = D / 8;  // 16-byte chunks per row
-  for (int i = tid; i < BQ * CH; i += 128) {
+  for (int i = tid; i < BQ * CH; i += NT) {
     const int r = i / CH, ch = i - r * CH;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (q0 + r < a.S) v = *(const uint4*)(qbase + (q0 + r) * (int64_t)a.nh * D + ch * 8);
@@ -67,20 +70,32 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
   const uint32_t sv_u = (uint32_t)__cvta_generic_to_shared(sv);
   const float LOG2E = 1.4426950408889634f;
 
+  // asynchronous copy of key/value tile kt into buffer buf (rows past the context are zero)
+  auto load_kv = [&](int buf, int64_t kt) {
+    const int64_t k0 = kt * BKV;
+    for (int i = tid; i < BKV * CH; i += NT) {
+      const int r = i / CH, ch = i - r * CH;
+      const bool in = k0 + r < kv_len;
+      const int64_t off = in ? (k0 + r) * (int64_t)D + ch * 8 : 0;
+      const uint32_t d = (uint32_t)(((buf * BKV + r) * LD + ch * 8) * 2);
+      cp_async16(sk_u + d, kbase + off, in ? 16 : 0);
+      cp_async16(sv_u + d, vbase + off, in ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (kt0 <= kt1) load_kv(0, kt0);
+
   for (int64_t kt = kt0; kt <= kt1; ++kt) {
     const int64_t k0 = kt * BKV;
-    __syncthreads();  // previous tile fully consumed (and Q stored, first time)
-    for (int i = tid; i < BKV * CH; i += 128) {
-      const int r = i / CH, ch = i - r * CH;
-      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (k0 + r < kv_len) {
-        kv = *(const uint4*)(kbase + (k0 + r) * (int64_t)D + ch * 8);
-        vv = *(const uint4*)(vbase + (k0 + r) * (int64_t)D + ch * 8);
-      }
-      *(uint4*)(sk + r * LD + ch * 8) = kv;
-      *(uint4*)(sv + r * LD + ch * 8) = vv;
+    const int buf = NBUF == 2 ? (int)((kt - kt0) & 1) : 0;
+    if (NBUF == 2 && kt < kt1) {
+      load_kv(buf ^ 1, kt + 1);  // that buffer was last read two tiles ago, before the barrier that ended the previous tile
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
-    __syncthreads();
+    __syncthreads();  // tile kt (and, the first time, Q) visible to every warp
+    const uint32_t sk_b = sk_u + (uint32_t)(buf * BKV * LD * 2), sv_b = sv_u + (uint32_t)(buf * BKV * LD * 2);
 
     // S = Q K^T for this warp's 16 rows x 64 keys
     float s[BKV / 8][4];
@@ -99,7 +114,7 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
         uint32_t b0, b1, b2, b3;
         const int key = j * 8 + (lane & 7) + 8 * (lane >> 4);
         const int col = kk * 16 + 8 * ((lane >> 3) & 1);
-        ldsm_x4(sk_u + (key * LD + col) * 2, b0, b1, b2, b3);
+        ldsm_x4(sk_b + (key * LD + col) * 2, b0, b1, b2, b3);
         mma_bf16(s[j], a0, a1, a2, a3, b0, b1);
         mma_bf16(s[j + 1], a0, a1, a2, a3, b2, b3);
       }
@@ -167,11 +182,13 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
         uint32_t b0, b1, b2, b3;
         const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
         const int col = j * 8 + 8 * (lane >> 4);
-        ldsm_x4_t(sv_u + (key * LD + col) * 2, b0, b1, b2, b3);
+        ldsm_x4_t(sv_b + (key * LD + col) * 2, b0, b1, b2, b3);
         mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
         mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
       }
     }
+    __syncthreads();  // every warp is done with this buffer before a later copy overwrites it
+    if (NBUF == 1 && kt < kt1) load_kv(0, kt + 1);
   }
 
   // normalise and store
@@ -189,17 +206,17 @@ __global__ void __launch_bounds__(128) k_attn_prefill(AttnArgs a, float scale) {
   }
 }
 
-template <int D>
+template <int D, int BQ, int NBUF>
 int launch_prefill(cg_ctx* c, const AttnArgs& a) {
-  constexpr size_t smem = (size_t)3 * 64 * (D + 8) * 2;
+  constexpr size_t smem = (size_t)(BQ + 2 * NBUF * 64) * (D + 8) * 2;
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_attn_prefill<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_attn_prefill<D, BQ, NBUF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid((unsigned)((a.S + 63) / 64), (unsigned)a.nh, (unsigned)a.B);
+  dim3 grid((unsigned)((a.S + BQ - 1) / BQ), (unsigned)a.nh, (unsigned)a.B);
   const float scale = 1.0f / sqrtf((float)D);
-  CG_CUDA(c, launch_kernel(c, k_attn_prefill<D>, grid, dim3(128), smem, 1, a, scale));
+  CG_CUDA(c, launch_kernel(c, k_attn_prefill<D, BQ, NBUF>, grid, dim3(BQ * 2), smem, 1, a, scale));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -218,9 +235,9 @@ int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a) {
   CG_TRY(check(c, a));
   if (a.B == 0 || a.S == 0) return CG_OK;
   switch (a.d) {
-    case 64: return launch_prefill<64>(c, a);
-    case 128: return launch_prefill<128>(c, a);
-    default: return launch_prefill<256>(c, a);
+    case 64: return launch_prefill<64, 128, 2>(c, a);
+    case 128: return launch_prefill<128, 128, 2>(c, a);
+    default: return launch_prefill<256, 64, 1>(c, a);
   }
 }
 
