@@ -341,6 +341,11 @@ int launch(cg_ctx* c, const AttnDecArgs& a) {
     CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
+  static bool wide = false;
+  if (!wide && a.splits > 8) {
+    CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    wide = true;
+  }
   dim3 grid((unsigned)a.nkv, (unsigned)a.B, (unsigned)a.splits);
   CG_CUDA(c, launch_kernel(c, k_attn_dec<D>, grid, dim3(128), smem, a.splits, a, 1.0f / sqrtf((float)D)));
   CG_LAUNCHED(c);
@@ -351,9 +356,13 @@ int launch(cg_ctx* c, const AttnDecArgs& a) {
 
 // context slices per (row, kv head): a power of two up to 8 (one portable cluster), about
 // 128 keys per slice at full context
-int attn_dec_splits(int64_t Tmax) {
+int attn_dec_splits(int64_t Tmax, int64_t pairs) {
   int s = 1;
   while (s < 8 && (int64_t)s * 128 < Tmax) s *= 2;
+  // (16 slices -- a cluster size this GPU supports beyond the portable 8 -- were measured for
+  // few (row, kv head) pairs with long contexts and were slower: 2.92 -> 3.15 ms per step on
+  // the 256-wide heads of the Gemma shape.)
+  (void)pairs;
   return s;
 }
 

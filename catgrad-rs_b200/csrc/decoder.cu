@@ -73,7 +73,6 @@ struct cg_decoder {
   cg_tensor *m_ids = nullptr, *m_wts = nullptr, *m_pos = nullptr, *m_tiles = nullptr, *m_xg = nullptr, *m_h = nullptr,
             *m_y = nullptr, *m_xs3 = nullptr, *m_logits = nullptr;
   int El = 0;                    // experts on this rank
-  int attn_splits = 1;
   bool pending_reduce = false;   // x still lacks the addends pushed by the last row-parallel GEMM
   bool logits_gathered = true;   // `logits` holds every rank's slice
   cudaGraphExec_t graph = nullptr;
@@ -316,7 +315,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
       f.nh = D->nh; f.nkv = D->nkv; f.d = D->d;
       f.window = windowed ? cfg.sliding_window : 0;
       f.softcap = cfg.attn_softcap;
-      f.splits = D->attn_splits;
+      f.splits = attn_dec_splits(cfg.max_seq, B * D->nkv);
       CG_TRY(k_launch_attn_dec(c, f));
     } else {
     RopeStoreArgs r;
@@ -668,7 +667,6 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   n = 2 * (int64_t)cfg.max_batch;  // one 64-bit argmax merge slot per row
   CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->best));
   CG_CUDA(c, cudaMemsetAsync(D->best->data(), 0, (size_t)n * 4, c->core->stream));
-  D->attn_splits = attn_dec_splits(cfg.max_seq);
 
   CG_TRY(ensure_workspace(D, cfg.max_batch));
   CG_TRY(set_state(D, 0, 0));

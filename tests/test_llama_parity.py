@@ -50,7 +50,13 @@ def checker_logits(oracle, cfg, params, ids_row):
     return oracle.to_numpy(lg)[0]  # [S, V]
 
 
-@pytest.mark.parametrize("cfg,batch,seq,steps", [(SMALL, 2, 24, 6), (SMALL_D128, 3, 70, 4), (SMALL, 1, 1, 5)])
+SMALL_D256 = synth.ModelConfig("small-llama-d256", 512, 768, 2, 2, 1, 1024, head_dim=256, rms_norm_eps=1e-5,
+                               rope_theta=500000.0, tie_word_embeddings=True, dtype="bf16")
+
+
+# the two long prompts exercise many key tiles per slice in the decode attention (8-slice clusters)
+@pytest.mark.parametrize("cfg,batch,seq,steps", [(SMALL, 2, 24, 6), (SMALL_D128, 3, 70, 4), (SMALL, 1, 1, 5),
+                                                 (SMALL_D128, 1, 2050, 2), (SMALL_D256, 2, 2050, 2)])
 def test_decoder_matches_checker(oracle, cuda_bf16, cfg, batch, seq, steps):
     C = cuda_bf16
     po = load(oracle, cfg)
