@@ -317,14 +317,24 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
   const uint32_t po_u = (uint32_t)__cvta_generic_to_shared(part_o);
   for (int i = tid + 128 * split; i < rep * D; i += 128 * S) {
     const int r = i / D;
+    // all remote loads first (their latencies overlap), then the arithmetic; S <= 8
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const bool in = s < S;
+      ms[s] = in ? ld_dsmem(ml_u + (uint32_t)(2 * r) * 4u, (uint32_t)s) : -INFINITY;
+      ls[s] = in ? ld_dsmem(ml_u + (uint32_t)(2 * r + 1) * 4u, (uint32_t)s) : 0.f;
+      os[s] = in ? ld_dsmem(po_u + (uint32_t)i * 4u, (uint32_t)s) : 0.f;
+    }
     float mm = -INFINITY;
-    for (int s = 0; s < S; ++s) mm = fmaxf(mm, ld_dsmem(ml_u + (uint32_t)(2 * r) * 4u, (uint32_t)s));
+#pragma unroll
+    for (int s = 0; s < 8; ++s) mm = fmaxf(mm, ms[s]);
     float ll = 0.f, oo = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = ld_dsmem(ml_u + (uint32_t)(2 * r) * 4u, (uint32_t)s);
-      const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
-      ll += ld_dsmem(ml_u + (uint32_t)(2 * r + 1) * 4u, (uint32_t)s) * f;
-      oo += ld_dsmem(po_u + (uint32_t)i * 4u, (uint32_t)s) * f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const float f = ms[s] == -INFINITY ? 0.f : __expf(ms[s] - mm);
+      ll += ls[s] * f;
+      oo += os[s] * f;
     }
     a.out[(b * a.nh + kvh * rep + r) * (int64_t)D + (i - r * D)] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
   }

@@ -74,6 +74,11 @@ struct cg_decoder {
             *m_y = nullptr, *m_xs3 = nullptr, *m_logits = nullptr;
   int El = 0;                    // experts on this rank
   bool pending_reduce = false;   // x still lacks the addends pushed by the last row-parallel GEMM
+  // norm hand-over (see DecGemm): xn holds bf16(x * gain) un-normalised and ss the per-CTA sums
+  // of squares the last residual GEMM wrote; the next GEMM applies 1 / rms in its epilogue
+  bool xn_raw = false;
+  int ss_parts = 0;
+  cg_tensor* ss = nullptr;
   bool logits_gathered = true;   // `logits` holds every rank's slice
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
@@ -213,12 +218,27 @@ int moe_block(cg_decoder* D, Layer& L, int64_t M) {
 // the tiled kernel.
 bool small_m(int64_t M, int64_t K) { return gemm_dec_supported(M, K); }
 
+constexpr int SS_MAX_PARTS = 4096;
+
 int gemm(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, void* out, const float* residual, int mode,
-         bool dual = false) {
+         bool dual = false, const cg_tensor* produce_gain = nullptr, bool consume = false) {
   const int64_t K = w->dims[1];
   const int64_t N = dual ? w->dims[0] / 2 : w->dims[0];
   if (small_m(M, K)) {
     DecGemm g;
+    if (consume) {
+      g.ss_in = (const float*)D->ss->data();
+      g.ss_parts = D->ss_parts;
+      g.ss_eps = D->cfg.rms_eps;
+    }
+    if (produce_gain) {
+      g.xb_out = (__nv_bfloat16*)D->xn->data();
+      g.g_next = (const float*)produce_gain->data();
+      g.g_plus_one = D->cfg.norm_plus_one;
+      g.ss_out = (float*)D->ss->data();
+      D->ss_parts = gemm_dec_ss_parts(N, K);
+      if (D->ss_parts > SS_MAX_PARTS) return fail(D->c, CG_ERR_UNSUPPORTED, "decoder: too many partial sums for the norm hand-over");
+    }
     g.x = (const __nv_bfloat16*)xin->data(); g.ldx = K;
     g.w = (const __nv_bfloat16*)w->data(); g.ldw = K; g.w_rows = w->dims[0];
     g.out = out; g.ldo = N; g.residual = residual; g.out_mode = mode;
@@ -286,17 +306,23 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
   const bool push = use_push(D, M, S);
   const PeerPush px = push ? peer_push_of(c->xchg) : PeerPush{};
   D->pending_reduce = false;
+  // norm hand-over between GEMMs: decode steps of pre-norm models on one GPU
+  const bool handover = c->opt_handover && S == 1 && small_m(M, D->H) && cfg.tp_world == 1 && !cfg.post_norms;
+  D->xn_raw = false;
   for (int li = 0; li < cfg.num_layers; ++li) {
     Layer& L = D->layers[li];
     const bool small = small_m(M, D->H);
-    if (D->pending_reduce)
+    if (D->xn_raw) {
+      // the previous layer's down projection already left bf16(x * gain) and the sums of squares
+    } else if (D->pending_reduce)
       CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                                      cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     else
       CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                               cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     D->pending_reduce = false;
-    CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0));
+    CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0, false, nullptr, D->xn_raw));
+    D->xn_raw = false;
     const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
     if (S == 1) {
       AttnDecArgs f;
@@ -346,13 +372,22 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     a.scratch = nullptr;
     CG_TRY(k_launch_attn_prefill(c, a));
     }
-    CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push));
+    if (!(handover && !L.moe)) CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push));
     if (push) {
       CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                                      cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
       CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
       CG_TRY(project_add(D, D->hact, M, L.w_down, nullptr, true));
       D->pending_reduce = true;
+      continue;
+    }
+    if (handover && !L.moe) {
+      float* x = (float*)D->x->data();
+      CG_TRY(gemm(D, D->att, M, L.w_o, x, x, 2, false, L.ln_pre_ffn));
+      CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true, nullptr, true));
+      const cg_tensor* next_gain = li + 1 < cfg.num_layers ? D->layers[li + 1].ln_in : D->ln_f;
+      CG_TRY(gemm(D, D->hact, M, L.w_down, x, x, 2, false, next_gain));
+      D->xn_raw = true;
       continue;
     }
     if (L.moe) {
@@ -375,6 +410,15 @@ int run_head(cg_decoder* D, int64_t B, int64_t S, bool advance) {
   const cg_decoder_config& cfg = D->cfg;
   float* lg = (float*)D->logits->data();
   float* mine = lg + (int64_t)cfg.tp_rank * B * D->Vp;
+  if (D->xn_raw) {
+    // decode step with the norm hand-over (S == 1): the LM head reads bf16(x * gain) and scales
+    D->xn_raw = false;
+    CG_TRY(gemm(D, D->xn, B, D->head, mine, nullptr, 0, false, nullptr, true));
+    D->logits_gathered = true;
+    return k_launch_argmax(c, lg, B, D->Vp, cfg.tp_world, cfg.final_softcap, (uint32_t*)D->cur->data(),
+                           (uint32_t*)D->history->data(), cfg.max_seq, D->count_dev(), D->pos_dev(), advance ? 1 : 0,
+                           (unsigned long long*)D->best->data());
+  }
   if (D->pending_reduce) {
     // decode step on the push path: S == 1
     const PeerPush px = peer_push_of(c->xchg);
@@ -497,7 +541,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
-  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best);
+  drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best); drop(D->ss);
   drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
   drop(D->m_xs3); drop(D->m_logits);
   delete D;
@@ -664,6 +708,8 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   n = std::max<int64_t>(32 * 64 * widest, (int64_t)300 * 128 * 256);
   CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->splitk));
   D->splitk_floats = n;
+  n = (int64_t)SS_MAX_PARTS * 32;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &D->ss));
   n = 2 * (int64_t)cfg.max_batch;  // one 64-bit argmax merge slot per row
   CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->best));
   CG_CUDA(c, cudaMemsetAsync(D->best->data(), 0, (size_t)n * 4, c->core->stream));

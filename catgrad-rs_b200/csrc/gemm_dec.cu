@@ -42,7 +42,18 @@ struct DecArgs {
   int trace;  // slot in the timeline buffer, or -1
   PeerPush push;  // out_mode 3
   int total_ctas;
+  // norm hand-over (see DecGemm): producer side ...
+  __nv_bfloat16* xb_out;
+  const float* g_next;
+  int g_plus_one;
+  float* ss_out;
+  // ... and consumer side
+  const float* ss_in;
+  int ss_parts;
+  float ss_inv_h, ss_eps;
 };
+
+constexpr int SQ_FLOATS = 2048;  // per-CTA staging of squared outputs (cluster epilogue)
 
 // Timeline of the decode GEMM launches (diagnostics): per slot {first CTA start, predecessor
 // complete, last accumulator ready, last CTA end} in globaltimer nanoseconds.
@@ -56,19 +67,33 @@ __device__ __forceinline__ void trace_max(int slot, int f) {
   if (slot >= 0) atomicMax(&g_trace[slot * 4 + f], (unsigned long long)globaltimer());
 }
 
-__device__ __forceinline__ void finish(const DecArgs& p, int m, int n, float g, float u, uint32_t parity) {
+__device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g, float u, uint32_t parity, const float* sc) {
+  if (p.ss_in) {  // the activations were handed over un-normalised: the row's 1 / rms goes here
+    g *= sc[m];
+    u *= sc[m];
+  }
   float v = g;
   if (p.dual) v = (p.act == 0 ? silu_f(g) : gelu_f(g)) * u;
   const int64_t o = (int64_t)m * p.ldo + n;
+  if (p.xb_out) {
+    // residual epilogue that also prepares the next norm: the new residual in f32, its
+    // gain-scaled bf16 copy for the next GEMM, and its square for the row's sum of squares
+    const float r = v + p.residual[o];
+    ((float*)p.out)[o] = r;
+    const float gn = p.g_plus_one ? 1.f + p.g_next[n] : p.g_next[n];
+    p.xb_out[o] = __float2bfloat16_rn(r * gn);
+    return r * r;
+  }
   if (p.out_mode == 3) {
     // this rank's addend goes into slot [parity][rank] of every rank's exchange area
     const int64_t slot = ((int64_t)parity * p.push.world + p.push.rank) * p.push.max_elems + o;
     for (int r = 0; r < p.push.world; ++r) p.push.data[r][slot] = v;
-    return;
+    return 0.f;
   }
   if (p.out_mode == 0) ((float*)p.out)[o] = v;
   else if (p.out_mode == 1) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
   else ((float*)p.out)[o] = v + p.residual[o];
+  return 0.f;
 }
 
 template <int TN>
@@ -89,6 +114,10 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   const uint32_t bar_accum = bars + 16 * STAGES;
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen + boff + 16 * STAGES + 8);
   volatile int* cta_abort = (volatile int*)(gen + boff + 16 * STAGES + 12);
+  float* sc = (float*)(gen + boff + 16 * 8 + 64);  // [32] per-token 1 / rms (consumer side)
+  // [SQ_FLOATS] squared outputs (producer side): in the ring, which is idle by then, behind the
+  // staging area of the cluster reduction
+  float* sq = (float*)(gen + 2 * TN * BM * 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BM, split = blockIdx.z;
@@ -174,6 +203,18 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   } else {
     // outputs (and the residual) belong to the stream order: wait for the preceding kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.ss_in) {
+      // per-token sum of squares = the producer's per-CTA partials added in a fixed order
+      // (four interleaved quarters per token, then the quarters): loads fly while the MMAs run
+      const int et = tid - 64, m = et >> 2, j = et & 3;
+      float a = 0.f;
+      if (m < p.M)
+        for (int i = j; i < p.ss_parts; i += 4) a += __ldcg(p.ss_in + (int64_t)i * 32 + m);
+      const float a1 = __shfl_down_sync(0xffffffffu, a, 1), a2 = __shfl_down_sync(0xffffffffu, a, 2),
+                  a3 = __shfl_down_sync(0xffffffffu, a, 3);
+      if (j == 0 && m < p.M) sc[m] = 1.0f / sqrtf((((a + a1) + a2) + a3) * p.ss_inv_h + p.ss_eps);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     if (nkb > 0) {
       acc_ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -204,14 +245,26 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
           stage[(c0 + j) * BM + row] = __uint_as_float(g[j]);
           if (p.dual) stage[(TN + c0 + j) * BM + row] = __uint_as_float(u[j]);
         }
-      } else if (n < p.N) {
+      } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j >= p.M) break;
-          finish(p, c0 + j, n, __uint_as_float(g[j]), p.dual ? __uint_as_float(u[j]) : 0.f, parity);
+          float r2 = 0.f;
+          if (n < p.N) r2 = finish(p, c0 + j, n, __uint_as_float(g[j]), p.dual ? __uint_as_float(u[j]) : 0.f, parity, sc);
+          if (p.ss_out) {
+            // one CTA per tile here: the tile's 128 rows are summed per token, warp tree then warps in order
+            for (int o = 16; o; o >>= 1) r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+            if (lane == 0) sq[q * 32 + c0 + j] = r2;
+          }
         }
       }
     }
+  }
+  if (warp >= 2 && p.ss_out && !cluster) {
+    // (outside the branch above: all four epilogue warps must reach this barrier)
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    const int et = tid - 64;
+    if (acc_ok && et < p.M) p.ss_out[(int64_t)blockIdx.x * 32 + et] = ((sq[et] + sq[32 + et]) + sq[64 + et]) + sq[96 + et];
   }
 
   if (cluster) {
@@ -224,13 +277,21 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
       for (int e = tid - 64; e < rows_per * cols; e += 128) {
         const int col = e / rows_per;
         const int row = split * rows_per + (e - col * rows_per);
-        float g = 0.f, u = 0.f;
-        for (int s = 0; s < S; ++s) {
-          g += ld_cluster_f32(base + (uint32_t)(col * BM + row) * 4u, (uint32_t)s);
-          if (p.dual) u += ld_cluster_f32(base + (uint32_t)((TN + col) * BM + row) * 4u, (uint32_t)s);
-        }
+        const float g = sum_cluster_f32(base + (uint32_t)(col * BM + row) * 4u, S);
+        const float u = p.dual ? sum_cluster_f32(base + (uint32_t)((TN + col) * BM + row) * 4u, S) : 0.f;
         const int n = n0 + row;
-        if (n < p.N) finish(p, col, n, g, u, parity);
+        float r2 = 0.f;
+        if (n < p.N) r2 = finish(p, col, n, g, u, parity, sc);
+        if (p.ss_out) sq[e] = r2;  // e = col * rows_per + local row
+      }
+      if (p.ss_out) {
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const int et = tid - 64;
+        if (et < cols) {
+          float a = 0.f;
+          for (int i = 0; i < rows_per; ++i) a += sq[et * rows_per + i];
+          p.ss_out[((int64_t)blockIdx.x * S + split) * 32 + et] = a;
+        }
       }
     }
     __syncwarp();
@@ -278,6 +339,21 @@ int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const De
 
 bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 8 == 0; }
 
+// split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this GPU
+// supports), about two CTAs per SM in total, at least two k blocks per CTA
+static int dec_splits(int64_t tiles, int kb_total) {
+  int splits = 1;
+  while (splits < 16 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  if ((kb_total + kb_per - 1) / kb_per != splits) splits = 1;  // an empty slice would break the cluster shape
+  return splits;
+}
+
+int gemm_dec_ss_parts(int64_t N, int64_t K) {
+  const int64_t tiles = (N + BM - 1) / BM;
+  return (int)(tiles * dec_splits(tiles, (int)((K + BK - 1) / BK)));
+}
+
 int gemm_dec(cg_ctx* c, const DecGemm& g) {
   if (g.M <= 0 || g.N <= 0) return CG_OK;
   if (!gemm_dec_supported(g.M, g.K) || g.K <= 0 || g.ldw % 8 || g.ldx % 8 || ((uintptr_t)g.w % 16) || ((uintptr_t)g.x % 16))
@@ -285,15 +361,8 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   const int tn = g.M <= 16 ? 16 : 32;
   const int64_t tiles = (g.N + BM - 1) / BM;
   const int kb_total = (int)((g.K + BK - 1) / BK);
-  // split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this
-  // GPU supports), about two CTAs per SM in total, at least two k blocks per CTA
-  int splits = 1;
-  while (splits < 16 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
-  int kb_per = (kb_total + splits - 1) / splits;
-  if ((kb_total + kb_per - 1) / kb_per != splits) {  // an empty slice would break the cluster shape
-    splits = 1;
-    kb_per = kb_total;
-  }
+  const int splits = dec_splits(tiles, kb_total);
+  const int kb_per = (kb_total + splits - 1) / splits;
   const size_t wbytes = g.dual ? 2 * A_BYTES : A_BYTES;
   const size_t stage = wbytes + (size_t)tn * BK * 2;
   // about a third of an SM's shared memory per CTA, so the next GEMM's CTAs can be resident
@@ -302,9 +371,10 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   int stages = (int)std::max<size_t>(2, budget / stage);
   stages = std::min(stages, std::max(kb_per, 2));
   stages = std::min(stages, 8);
-  const size_t stage_need = (size_t)(g.dual ? 2 : 1) * tn * BM * 4;  // cluster-reduce staging lives in the ring
-  while (splits > 1 && stage_need > (size_t)stages * stage) ++stages;
-  const size_t smem = (size_t)stages * stage + 1024 + 16 * 8 + 64;
+  // cluster-reduce staging and the squared-output staging of the norm hand-over live in the ring
+  const size_t stage_need = (size_t)2 * tn * BM * 4 + (g.ss_out ? (size_t)SQ_FLOATS * 4 : 0);
+  while ((splits > 1 || g.ss_out) && stage_need > (size_t)stages * stage) ++stages;
+  const size_t smem = (size_t)stages * stage + 1024 + 16 * 8 + 64 + 128;
 
   CUtensorMap mw, mx;
   CG_TRY(make_map(c, &mw, g.w, g.w_rows, g.K, g.ldw, BM));
@@ -317,6 +387,10 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   a.err = c->core->dev_err;
   a.trace = c->trace_on ? (int)(c->trace_next++ % TRACE_SLOTS) : -1;
   a.total_ctas = (int)(tiles * splits);
+  a.xb_out = g.xb_out; a.g_next = g.g_next; a.g_plus_one = g.g_plus_one; a.ss_out = g.ss_out;
+  a.ss_in = g.ss_in; a.ss_parts = g.ss_parts; a.ss_inv_h = g.ss_in ? 1.0f / (float)g.K : 0.f; a.ss_eps = g.ss_eps;
+  if (g.xb_out && (g.out_mode != 2 || g.dual || !g.g_next || !g.ss_out || g.ldo != g.N))
+    return fail(c, CG_ERR_INVALID, "gemm_dec: the norm hand-over needs the residual epilogue on a dense output");
   if (g.out_mode == 3) {
     if (!g.push || g.dual || g.M * g.ldo > g.push->max_elems)
       return fail(c, CG_ERR_INVALID, "gemm_dec: the pushed addend does not fit the exchange area");

@@ -268,8 +268,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       for (int e = tid - 64; e < rows_per * cols; e += 128) {
         const int col = e / rows_per;
         const int row = split * rows_per + (e - col * rows_per);
-        float acc = 0.f;
-        for (int s = 0; s < S; ++s) acc += ld_cluster_f32(stage_u + (uint32_t)(col * BM + row) * 4u, (uint32_t)s);
+        const float acc = sum_cluster_f32(stage_u + (uint32_t)(col * BM + row) * 4u, S);
         const int n = n0 + row;
         if (n < p.N) store_out(p, m0 + col, n, acc);
       }

@@ -136,11 +136,24 @@ struct DecGemm {
   int out_mode;             // 0: f32, 1: bf16, 2: f32 out = product + residual,
                             // 3: the product is pushed as this rank's addend of an all-reduce (out unused)
   const PeerPush* push;     // for out_mode 3
+  // Norm hand-over between consecutive GEMMs (RMSNorm(x) W^T = (x g) W^T / rms(x) row by row):
+  // a residual GEMM (out_mode 2) that is followed by a norm can also write xb_out = bf16(out * g)
+  // (g = g_next, or 1 + g_next) and ss_out[part][32] = per-CTA sums of out^2 per token; the GEMM
+  // after the norm then reads xb as its activations and multiplies row m of its accumulators by
+  // 1 / sqrt(sum_parts ss_in[part][m] / K + ss_eps).  All null / zero = off.
+  __nv_bfloat16* xb_out = nullptr;
+  const float* g_next = nullptr;
+  int g_plus_one = 0;
+  float* ss_out = nullptr;
+  const float* ss_in = nullptr;
+  int ss_parts = 0;
+  float ss_eps = 0.f;
   int dual;                 // 1: rows n and n + N of w form gate and up; out = act(gate) * up
   int act;                  // 0 silu, 1 tanh-gelu
   int64_t M, N, K;
 };
 int gemm_dec(cg_ctx* c, const DecGemm& g);
+int gemm_dec_ss_parts(int64_t N, int64_t K);  // partials per token a hand-over producer with this shape writes
 bool gemm_dec_supported(int64_t M, int64_t K);
 
 // Mixture-of-experts feed-forward block (catgrad-llm/src/models/qwen3.rs:64-133) on M tokens:

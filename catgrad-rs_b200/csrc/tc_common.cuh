@@ -108,6 +108,18 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
   return v;
 }
 
+// Sum over the `n` (<= 16) CTAs of a cluster of the float at the same shared-memory offset, in
+// rank order.  All loads are issued before the first add, so their latencies overlap (a loop
+// of "load, add" would pay one distributed-shared-memory round trip per rank).
+__device__ __forceinline__ float sum_cluster_f32(uint32_t local_addr, int n) {
+  float v[16];
+#pragma unroll
+  for (int s = 0; s < 16; ++s) v[s] = s < n ? ld_cluster_f32(local_addr, (uint32_t)s) : 0.f;
+  float acc = 0.f;
+#pragma unroll
+  for (int s = 0; s < 16; ++s) acc += v[s];  // adding the zeros of absent ranks changes nothing
+  return acc;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

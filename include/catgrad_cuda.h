@@ -163,6 +163,9 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "pdl"   : 1 (default) = fused kernels are launched with programmatic stream serialization
  *   "persistent" : 1 (default) = GEMMs with several output tiles per SM run as one resident
  *             CTA per SM with double-buffered accumulators; 0 = one CTA per tile
+ *   "handover" : 1 (default) = in decode steps of pre-norm models the residual GEMMs also leave
+ *             the gain-scaled bf16 activations and per-row sums of squares, and the next GEMM
+ *             applies 1 / rms in its epilogue (no separate norm kernel); 0 = norm kernels
  *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
  *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
  *             decode step, and identically on every rank.
