@@ -43,12 +43,43 @@ struct TcpArgs {
   int m_tiles, n_tiles;
   int row2_off;   // PAIR: rows between a gate row and its up row
   int act;        // PAIR: 0 silu, 1 tanh-gelu
+  // GROUPED (mixture-of-experts): token tiles come from a device-built list, each belonging to
+  // one expert whose weights start at row expert * w_rows of the stacked matrix; rows of a tile
+  // past `tile_rows` belong to other experts and are not stored
+  const int32_t* tile_expert;
+  const int32_t* tile_row0;
+  const int32_t* tile_rows;
+  const int32_t* n_list;
+  int w_rows;
   int32_t* err;
 };
 
-template <int TN, int PAIR, int STAGES>
+struct TileAt {
+  int m0, m_end, n0, wrow;
+};
+
+template <int TN, int GROUPED>
+__device__ __forceinline__ TileAt tile_at(const TcpArgs& p, int t) {
+  TileAt a;
+  if (GROUPED) {
+    const int te = t / p.n_tiles;
+    a.n0 = (t - te * p.n_tiles) * BM;
+    a.m0 = p.tile_row0[te];
+    a.m_end = a.m0 + p.tile_rows[te];
+    a.wrow = p.tile_expert[te] * p.w_rows + a.n0;
+  } else {
+    a.m0 = (t % p.m_tiles) * TN;
+    a.m_end = p.M;
+    a.n0 = (t / p.m_tiles) * BM;
+    a.wrow = a.n0;
+  }
+  return a;
+}
+
+template <int TN, int PAIR, int STAGES, int GROUPED>
 __global__ void __launch_bounds__(192, 1)
-k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcpArgs p) {
+k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u,
+           const __grid_constant__ CUtensorMap map_x, TcpArgs p) {
   constexpr uint32_t B_BYTES = TN * BK * 2;
   constexpr uint32_t W_BYTES = A_BYTES * (1 + PAIR);
   constexpr uint32_t STAGE_BYTES = W_BYTES + B_BYTES;
@@ -69,7 +100,6 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   volatile int* cta_abort = (volatile int*)(gen + STAGES * STAGE_BYTES + 16 * STAGES + 36);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
   const int nkb = p.kb_total;
 
   if (tid == 0) {
@@ -96,15 +126,16 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // activations, the residual and the output belong to the stream order
+  // activations, the residual, the output (and the tile list) belong to the stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int total_tiles = (GROUPED ? *p.n_list : p.m_tiles) * p.n_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % p.m_tiles) * TN, n0 = (t / p.m_tiles) * BM;
+        const TileAt ta = tile_at<TN, GROUPED>(p, t);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (it >= STAGES) {
@@ -114,9 +145,9 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
           const uint32_t full = bars + 8 * s;
           const uint32_t a = base + s * STAGE_BYTES;
           mbar_expect_tx(full, STAGE_BYTES);
-          tma_load_2d(a, &map_w, kb * BK, n0, full);
-          if (PAIR) tma_load_2d(a + A_BYTES, &map_w, kb * BK, n0 + p.row2_off, full);
-          tma_load_2d(a + W_BYTES, &map_x, kb * BK, m0, full);
+          tma_load_2d(a, &map_w, kb * BK, ta.wrow, full);
+          if (PAIR) tma_load_2d(a + A_BYTES, GROUPED ? &map_u : &map_w, kb * BK, GROUPED ? ta.wrow : ta.wrow + p.row2_off, full);
+          tma_load_2d(a + W_BYTES, &map_x, kb * BK, ta.m0, full);
         }
       }
     }
@@ -158,15 +189,16 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++ti) {
       const uint32_t buf = (uint32_t)ti & 1u;
-      const int m0 = (t % p.m_tiles) * TN, n0 = (t / p.m_tiles) * BM;
-      const int n = n0 + row;
+      const TileAt ta = tile_at<TN, GROUPED>(p, t);
+      const int m0 = ta.m0, m_end = ta.m_end;
+      const int n = ta.n0 + row;
       ok = mbar_wait(bar_acc_full + 8 * buf, ((uint32_t)ti >> 1) & 1u, cta_abort, p.err);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 16) {
-        if (m0 + c0 >= p.M) break;
+        if (m0 + c0 >= m_end) break;
         uint32_t v[16];
         tmem_ld16(acc + (uint32_t)c0, v);
         if (PAIR) {
@@ -177,7 +209,7 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + c0 + j;
-              if (m >= p.M) break;
+              if (m >= m_end) break;
               const float g = __uint_as_float(v[j]);
               const float h = (p.act == 0 ? silu_f(g) : gelu_f(g)) * __uint_as_float(u[j]);
               ((__nv_bfloat16*)p.out)[(int64_t)m * p.ldo + n] = __float2bfloat16_rn(h);
@@ -192,18 +224,18 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c0 + j;
-                res[j] = m < p.M ? p.residual[(int64_t)m * p.ldo + n] : 0.f;
+                res[j] = m < m_end ? p.residual[(int64_t)m * p.ldo + n] : 0.f;
               }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c0 + j;
-                if (m < p.M) ((float*)p.out)[(int64_t)m * p.ldo + n] = __uint_as_float(v[j]) + res[j];
+                if (m < m_end) ((float*)p.out)[(int64_t)m * p.ldo + n] = __uint_as_float(v[j]) + res[j];
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c0 + j;
-                if (m >= p.M) break;
+                if (m >= m_end) break;
                 if (p.out_mode == 0) ((float*)p.out)[(int64_t)m * p.ldo + n] = __uint_as_float(v[j]);
                 else ((__nv_bfloat16*)p.out)[(int64_t)m * p.ldo + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
               }
@@ -225,15 +257,15 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   }
 }
 
-template <int TN, int PAIR, int STAGES>
-int launch_tcp(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const TcpArgs& a, int ctas) {
+template <int TN, int PAIR, int STAGES, int GROUPED>
+int launch_tcp(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, const TcpArgs& a, int ctas) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES * (1 + PAIR) + TN * BK * 2) + 1024 + 16 * STAGES + 64;
   static bool configured = false;
   if (!configured) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tcp<TN, PAIR, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tcp<TN, PAIR, STAGES, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  CG_CUDA(c, launch_kernel(c, k_gemm_tcp<TN, PAIR, STAGES>, dim3((unsigned)ctas), dim3(192), smem, 1, mw, mx, a));
+  CG_CUDA(c, launch_kernel(c, k_gemm_tcp<TN, PAIR, STAGES, GROUPED>, dim3((unsigned)ctas), dim3(192), smem, 1, mw, mu, mx, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -273,12 +305,44 @@ int gemm_tcp(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16
   a.n_tiles = (int)((N + BM - 1) / BM);
   a.row2_off = (int)N;
   a.act = act;
+  a.tile_expert = a.tile_row0 = a.tile_rows = a.n_list = nullptr;
+  a.w_rows = 0;
   a.err = c->core->dev_err;
   const int64_t tiles = (int64_t)a.m_tiles * a.n_tiles;
   if (tiles > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tcp: too many tiles");
   const int ctas = (int)std::min<int64_t>(tiles, sm_count(c));
-  if (pair) return launch_tcp<128, 1, 4>(c, mw, mx, a, ctas);
-  return launch_tcp<256, 0, 4>(c, mw, mx, a, ctas);
+  if (pair) return launch_tcp<128, 1, 4, 0>(c, mw, mw, mx, a, ctas);
+  return launch_tcp<256, 0, 4, 0>(c, mw, mw, mx, a, ctas);
+}
+
+// Grouped (mixture-of-experts) form over a device-built list of 128-token tiles; see
+// moe.cu.  w (and w_up when pair) are the experts' matrices stacked along the rows
+// ([experts * N, K]); x holds the grouped activation rows; out rows follow x.
+int gemm_tcp_grouped(cg_ctx* c, const __nv_bfloat16* x, int64_t x_rows, const __nv_bfloat16* w, const __nv_bfloat16* w_up,
+                     int64_t experts, void* out, int64_t N, int64_t K, int pair, int act, const int32_t* tile_expert,
+                     const int32_t* tile_row0, const int32_t* tile_rows, const int32_t* n_list, int64_t max_list) {
+  if (x_rows <= 0 || N <= 0 || experts <= 0) return CG_OK;
+  if (K <= 0 || K % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || (pair && ((uintptr_t)w_up % 16)))
+    return fail(c, CG_ERR_UNSUPPORTED, "gemm_tcp: k must be a multiple of 8, bases 16-byte aligned");
+  CUtensorMap mw, mu, mx;
+  CG_TRY(make_map(c, &mw, w, experts * N, K, K, BM));
+  CG_TRY(make_map(c, &mu, pair ? w_up : w, experts * N, K, K, BM));
+  CG_TRY(make_map(c, &mx, x, x_rows, K, K, 128));
+  TcpArgs a;
+  a.out = out; a.residual = nullptr; a.ldo = N;
+  a.M = (int)x_rows; a.N = (int)N; a.K = (int)K;
+  a.out_mode = pair ? 1 : 0;
+  a.kb_total = (int)((K + BK - 1) / BK);
+  a.m_tiles = 0;
+  a.n_tiles = (int)((N + BM - 1) / BM);
+  a.row2_off = 0;
+  a.act = act;
+  a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.tile_rows = tile_rows; a.n_list = n_list;
+  a.w_rows = (int)N;
+  a.err = c->core->dev_err;
+  const int ctas = (int)std::min<int64_t>(max_list * a.n_tiles, sm_count(c));
+  if (pair) return launch_tcp<128, 1, 4, 1>(c, mw, mu, mx, a, ctas);
+  return launch_tcp<128, 0, 6, 1>(c, mw, mu, mx, a, ctas);
 }
 
 }  // namespace cg

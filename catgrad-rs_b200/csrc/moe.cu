@@ -545,6 +545,17 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
   CG_TRY(make_map(c, &mx, a.w.xg, P, a.H, a.H, tn));
   g.out = a.w.h; g.ldo = a.Fe; g.N = a.Fe; g.w_rows = a.Fe; g.kb_total = (a.H + BK - 1) / BK;
   dim3 grid((unsigned)((a.Fe + BM - 1) / BM), (unsigned)max_tiles);
+  if (tn == 128 && c->opt_persistent) {
+    // many rows per expert: the persistent kernel (epilogue overlapped with the next tile)
+    CG_TRY(gemm_tcp_grouped(c, a.w.xg, P, a.w_gate, a.w_up, a.El, a.w.h, a.Fe, a.H, 1, a.act, a.w.tile_expert, a.w.tile_row0,
+                            a.w.tile_rows, a.w.n_tiles, max_tiles));
+    CG_TRY(gemm_tcp_grouped(c, a.w.h, P, a.w_down, nullptr, a.El, a.w.y, a.H, a.Fe, 0, 0, a.w.tile_expert, a.w.tile_row0,
+                            a.w.tile_rows, a.w.n_tiles, max_tiles));
+    CG_CUDA(c, launch_kernel(c, k_moe_combine, dim3(grid_for(a.M * (a.H / 4), 256)), dim3(256), 0, 1, (const float*)a.w.y,
+                             (const int32_t*)a.w.pos, (const float*)a.w.wts, a.M, a.k, a.H, a.add_residual, a.x, a.out));
+    CG_LAUNCHED(c);
+    return CG_OK;
+  }
   switch (tn) {
     case 16: CG_TRY((launch_moe_gemm<16, 1, 3, 2>(c, mw, mu, mx, g, grid))); break;
     case 32: CG_TRY((launch_moe_gemm<32, 1, 3, 1>(c, mw, mu, mx, g, grid))); break;

@@ -234,6 +234,9 @@ bool gemm_tcp_wanted(int64_t M, int64_t N, int64_t K);
 int gemm_tcp(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, int64_t w_rows,
              void* out, int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K, int out_mode,
              int pair, int act);
+int gemm_tcp_grouped(cg_ctx* c, const __nv_bfloat16* x, int64_t x_rows, const __nv_bfloat16* w, const __nv_bfloat16* w_up,
+                     int64_t experts, void* out, int64_t N, int64_t K, int pair, int act, const int32_t* tile_expert,
+                     const int32_t* tile_row0, const int32_t* tile_rows, const int32_t* n_list, int64_t max_list);
 // Gate and up projections with the activation fused: w holds the gate rows then the up rows
 // ([2 F, K]); out[M, F] (bf16) = act(x gate^T) * (x up^T), act 0 = silu, 1 = tanh-gelu.
 int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw,
