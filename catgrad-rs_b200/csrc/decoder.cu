@@ -77,6 +77,7 @@ struct cg_decoder {
   // norm hand-over (see DecGemm): xn holds bf16(x * gain) un-normalised and ss the per-CTA sums
   // of squares the last residual GEMM wrote; the next GEMM applies 1 / rms in its epilogue
   bool xn_raw = false;
+  bool xn_ready = false;         // xn already holds the normalised rows the next GEMM reads (post-norm models)
   int ss_parts = 0;
   cg_tensor* ss = nullptr;
   bool logits_gathered = true;   // `logits` holds every rank's slice
@@ -269,7 +270,8 @@ int all_reduce_f32(cg_decoder* D, float* p, int64_t n) {
 
 // x += W-projection of `xin` (row-split under tensor parallelism), optionally through a
 // post-norm: x += rmsnorm(proj).
-int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm, bool push) {
+int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm, bool push,
+                const cg_tensor* next_norm = nullptr) {
   cg_ctx* c = D->c;
   const bool tp = D->cfg.tp_world > 1;
   float* x = (float*)D->x->data();
@@ -287,6 +289,12 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
   }
   CG_TRY(gemm(D, xin, M, w, t, nullptr, 0));
   CG_TRY(all_reduce_f32(D, t, M * D->H));
+  if (next_norm) {
+    // the norm the next block starts with, in the same pass: xn is ready afterwards
+    D->xn_ready = true;
+    return k_launch_rmsnorm_add_norm(c, t, (const float*)post_norm->data(), (const float*)next_norm->data(), D->cfg.rms_eps,
+                                     D->cfg.norm_plus_one, M, D->H, x, (__nv_bfloat16*)D->xn->data());
+  }
   return k_launch_rmsnorm_add(c, t, (const float*)post_norm->data(), D->cfg.rms_eps, D->cfg.norm_plus_one, M, D->H, x);
 }
 
@@ -309,11 +317,12 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
   // norm hand-over between GEMMs: decode steps of pre-norm models on one GPU
   const bool handover = c->opt_handover && S == 1 && small_m(M, D->H) && cfg.tp_world == 1 && !cfg.post_norms;
   D->xn_raw = false;
+  D->xn_ready = false;
   for (int li = 0; li < cfg.num_layers; ++li) {
     Layer& L = D->layers[li];
     const bool small = small_m(M, D->H);
-    if (D->xn_raw) {
-      // the previous layer's down projection already left bf16(x * gain) and the sums of squares
+    if (D->xn_raw || D->xn_ready) {
+      // the previous layer's last kernel already left what the projection reads
     } else if (D->pending_reduce)
       CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                                      cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
@@ -321,6 +330,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
       CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_in->data(), cfg.rms_eps,
                               cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
     D->pending_reduce = false;
+    D->xn_ready = false;
     CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0, false, nullptr, D->xn_raw));
     D->xn_raw = false;
     const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
@@ -372,7 +382,8 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     a.scratch = nullptr;
     CG_TRY(k_launch_attn_prefill(c, a));
     }
-    if (!(handover && !L.moe)) CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push));
+    if (!(handover && !L.moe))
+      CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push, cfg.post_norms && !L.moe ? L.ln_pre_ffn : nullptr));
     if (push) {
       CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                                      cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
@@ -394,12 +405,15 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
       CG_TRY(moe_block(D, L, M));
       continue;
     }
-    CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
-                            cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    if (!D->xn_ready)
+      CG_TRY(k_launch_rmsnorm(c, (const float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
+                              cfg.norm_plus_one, M, D->H, D->xn->data(), 1));
+    D->xn_ready = false;
     // gate/up projections and act(gate) * up in one kernel
     CG_TRY(gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true));
     (void)small;
-    CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn, false));
+    CG_TRY(project_add(D, D->hact, M, L.w_down, L.ln_post_ffn, false,
+                       cfg.post_norms && li + 1 < cfg.num_layers ? D->layers[li + 1].ln_in : nullptr));
   }
   return CG_OK;
 }

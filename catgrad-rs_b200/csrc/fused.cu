@@ -94,6 +94,35 @@ __global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float
   }
 }
 
+// Post-norm layers (catgrad-llm/src/models/gemma3.rs:192-238): x += rmsnorm(y; g1), and in the
+// same pass the norm that the next block starts with, out = bf16(rmsnorm(x; g2)).  One block per row.
+__global__ void k_rmsnorm_add_norm(const float* y, const float* g1, const float* g2, float eps, int plus_one, int64_t H, float* x,
+                                   __nv_bfloat16* out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float sh[32];
+  const int64_t m = blockIdx.x;
+  const float* yr = y + m * H;
+  float* xr = x + m * H;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) ss += yr[i] * yr[i];
+  ss = block_sum(ss, sh);
+  const float rms1 = sqrtf(ss / (float)H + eps);
+  float s2 = 0.f;
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+    const float g = plus_one ? 1.f + g1[i] : g1[i];
+    const float v = xr[i] + yr[i] / rms1 * g;
+    xr[i] = v;
+    s2 += v * v;
+  }
+  s2 = block_sum(s2, sh);
+  const float rms2 = sqrtf(s2 / (float)H + eps);
+  for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+    const float g = plus_one ? 1.f + g2[i] : g2[i];
+    out[m * H + i] = __float2bfloat16_rn(xr[i] / rms2 * g);  // this thread's own store above
+  }
+}
+
 __global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* out) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -431,6 +460,15 @@ int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float ep
   if (M == 0) return CG_OK;
   const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   CG_CUDA(c, launch_kernel(c, k_rmsnorm<2>, dim3((unsigned)M), dim3(block), 0, 1, y, H, gamma, eps, plus_one, H, (void*)x));
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+int k_launch_rmsnorm_add_norm(cg_ctx* c, const float* y, const float* g1, const float* g2, float eps, int plus_one, int64_t M,
+                              int64_t H, float* x, __nv_bfloat16* out) {
+  if (M == 0) return CG_OK;
+  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  CG_CUDA(c, launch_kernel(c, k_rmsnorm_add_norm, dim3((unsigned)M), dim3(block), 0, 1, y, g1, g2, eps, plus_one, H, x, out));
   CG_LAUNCHED(c);
   return CG_OK;
 }

@@ -20,6 +20,11 @@ int k_launch_rmsnorm(cg_ctx* c, const float* x, int64_t ldx, const float* gamma,
 int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float eps, int plus_one, int64_t M, int64_t H,
                          float* x);
 
+// x += rmsnorm(y; g1) and, in the same pass, out = bf16(rmsnorm(x; g2)): a post-norm followed by
+// the next block's pre-norm.
+int k_launch_rmsnorm_add_norm(cg_ctx* c, const float* y, const float* g1, const float* g2, float eps, int plus_one, int64_t M,
+                              int64_t H, float* x, __nv_bfloat16* out);
+
 // act(gu[m, 0:F]) * gu[m, F:2F] -> bf16 [M, F]; act 0 = silu, 1 = tanh-gelu.
 int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out);
 

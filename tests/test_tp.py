@@ -96,7 +96,7 @@ GPU_WORKER = textwrap.dedent("""
     C = cg.CudaBackend(local, cg.PREC_BF16)
     cg.tp.init_comm(C, rank, world)
     C.set_option("peer", {peer})
-    cfg = cg.synth.ModelConfig("tp-gpu", 256, 512, 2, 4, 2, 1024, rope_theta=500000.0, tie_word_embeddings=True, dtype="bf16")
+    cfg = {cfg_expr}
     prompt = cg.synth.make_tokens(cfg, 3, 40, seed=2)
     dec = cg.Decoder(C, cfg, max_seq=64, max_batch=3, tp_rank=rank, tp_world=world)
     dec.load(cg.synth.make_weights(cfg, 0))
@@ -117,9 +117,16 @@ GPU_WORKER = textwrap.dedent("""
 """)
 
 
+DENSE_CFG = ('cg.synth.ModelConfig("tp-gpu", 256, 512, 2, 4, 2, 1024, rope_theta=500000.0, tie_word_embeddings=True, '
+             'dtype="bf16")')
+# mixture of experts: every rank owns 8 of the 16 experts, the partial sums meet in the all-reduce
+MOE_CFG = ('cg.synth.ModelConfig("ep-gpu", 128, 256, 2, 4, 2, 512, head_dim=64, arch="qwen3", rope_theta=1e6, dtype="bf16", '
+           'num_local_experts=16, num_experts_per_tok=4, moe_intermediate_size=96, norm_topk_prob=True)')
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("peer", [1, 0], ids=["peer-push", "nccl"])
-def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer):
+@pytest.mark.parametrize("peer,cfg_expr", [(1, DENSE_CFG), (0, DENSE_CFG), (0, MOE_CFG)], ids=["peer-push", "nccl", "experts"])
+def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer, cfg_expr):
     """peer=1: decode steps reduce over mapped peer memory (GEMM epilogue pushes, norm kernel
     sums); peer=0: NCCL all-reduce / all-gather.  Both must reproduce one GPU."""
     import torch
@@ -127,7 +134,7 @@ def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer):
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "tp.npy")
     script = tmp_path / "tp_gpu_worker.py"
-    script.write_text(GPU_WORKER.format(root=ROOT, out=out, peer=peer, want_peer=bool(peer)))
+    script.write_text(GPU_WORKER.format(root=ROOT, out=out, peer=peer, want_peer=bool(peer), cfg_expr=cfg_expr))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29612", str(script)],
@@ -135,7 +142,7 @@ def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = np.load(out)
     C = cg.CudaBackend(0, cg.PREC_BF16)
-    cfg = cg.synth.ModelConfig("tp-gpu", 256, 512, 2, 4, 2, 1024, rope_theta=500000.0, tie_word_embeddings=True, dtype="bf16")
+    cfg = eval(cfg_expr)
     prompt = cg.synth.make_tokens(cfg, 3, 40, seed=2)
     dec = cg.Decoder(C, cfg, max_seq=64, max_batch=3)
     dec.load(cg.synth.make_weights(cfg, 0))
