@@ -520,7 +520,9 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
     if (k.post_norms) return fail(c, CG_ERR_UNSUPPORTED, "decoder: expert layers with post-norms are not supported");
   }
   if (k.tp_rank < 0 || k.tp_rank >= W) return fail(c, CG_ERR_INVALID, "decoder: tp_rank out of range");
-  if (k.n_heads % k.n_kv_heads || k.n_heads % W || k.n_kv_heads % W || k.ffn % W || k.vocab % W)
+  // fewer kv heads than ranks: every kv head is replicated on W / n_kv_heads consecutive ranks
+  const bool kv_ok = k.n_kv_heads % W == 0 || (k.n_kv_heads < W && W % k.n_kv_heads == 0);
+  if (k.n_heads % k.n_kv_heads || k.n_heads % W || !kv_ok || k.ffn % W || k.vocab % W)
     return fail(c, CG_ERR_SHAPE, "decoder: heads, kv heads, ffn and vocab must divide by the tensor-parallel degree");
   if (k.hidden % 8 || (k.ffn / W) % 8 || (k.vocab / W) % 8 || k.head_dim % 8)
     return fail(c, CG_ERR_UNSUPPORTED, "decoder: hidden, ffn, vocab shards and head_dim must be multiples of 8");
@@ -531,7 +533,7 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
   D->cfg.tp_world = W;
   D->H = k.hidden;
   D->nh = k.n_heads / W;
-  D->nkv = k.n_kv_heads / W;
+  D->nkv = k.n_kv_heads >= W ? k.n_kv_heads / W : 1;
   D->d = k.head_dim;
   D->F = k.ffn / W;
   D->Vp = k.vocab / W;
@@ -637,8 +639,10 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
     int64_t s2[2] = {D->qkv, H};
     CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_qkv));
     CG_TRY(copy_block(c, wq, (int64_t)R * D->nh * d, D->nh * d, 0, H, L.w_qkv, 0));
-    CG_TRY(copy_block(c, wk, (int64_t)R * D->nkv * d, D->nkv * d, 0, H, L.w_qkv, D->nh * d));
-    CG_TRY(copy_block(c, wv, (int64_t)R * D->nkv * d, D->nkv * d, 0, H, L.w_qkv, (D->nh + D->nkv) * d));
+    // this rank's kv heads: its own share, or the one head its query heads belong to
+    const int64_t kv0 = nkv_all >= W ? (int64_t)R * D->nkv : (int64_t)R * nkv_all / W;
+    CG_TRY(copy_block(c, wk, kv0 * d, D->nkv * d, 0, H, L.w_qkv, D->nh * d));
+    CG_TRY(copy_block(c, wv, kv0 * d, D->nkv * d, 0, H, L.w_qkv, (D->nh + D->nkv) * d));
     s2[0] = H; s2[1] = D->nh * d;
     CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &L.w_o));
     CG_TRY(copy_block(c, wo, 0, H, (int64_t)R * D->nh * d, D->nh * d, L.w_o, 0));

@@ -124,8 +124,14 @@ MOE_CFG = ('cg.synth.ModelConfig("ep-gpu", 128, 256, 2, 4, 2, 512, head_dim=64, 
            'num_local_experts=16, num_experts_per_tok=4, moe_intermediate_size=96, norm_topk_prob=True)')
 
 
+# one kv head for two ranks: the head is replicated, each rank takes half of its query heads
+KVREP_CFG = ('cg.synth.ModelConfig("kvrep-gpu", 256, 512, 2, 4, 1, 1024, rope_theta=500000.0, tie_word_embeddings=True, '
+             'dtype="bf16")')
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("peer,cfg_expr", [(1, DENSE_CFG), (0, DENSE_CFG), (0, MOE_CFG)], ids=["peer-push", "nccl", "experts"])
+@pytest.mark.parametrize("peer,cfg_expr", [(1, DENSE_CFG), (0, DENSE_CFG), (0, MOE_CFG), (1, KVREP_CFG)],
+                         ids=["peer-push", "nccl", "experts", "kv-replicated"])
 def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer, cfg_expr):
     """peer=1: decode steps reduce over mapped peer memory (GEMM epilogue pushes, norm kernel
     sums); peer=0: NCCL all-reduce / all-gather.  Both must reproduce one GPU."""
