@@ -367,7 +367,9 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   const size_t stage = wbytes + (size_t)tn * BK * 2;
   // about a third of an SM's shared memory per CTA, so the next GEMM's CTAs can be resident
   // (and prefetching their weights) while this one computes
-  const size_t budget = 72 * 1024;
+  // (the paired gate/up GEMM carries two weight tiles per stage, so the same budget would
+  // leave it only two stages: it gets three, at two CTAs per SM)
+  const size_t budget = g.dual ? (tn == 32 ? 110 : 104) * 1024 : 72 * 1024;
   int stages = (int)std::max<size_t>(2, budget / stage);
   stages = std::min(stages, std::max(kb_per, 2));
   stages = std::min(stages, 8);
