@@ -160,3 +160,20 @@ def test_fused_attention(oracle, cuda, b, nh, nkv, s, d, window, cap):
     # probabilities are rounded to bf16 before the second product and the result is stored bf16
     np.testing.assert_allclose(got, want, rtol=0, atol=2e-2)
     assert np.abs(got - want).mean() < 3e-3
+
+
+@pytest.mark.gpu
+def test_randn_is_a_function_of_seed_and_index(cuda, cuda_bf16):
+    """cg_randn: counter-based normals -- same seed, same tensor; moments as asked; storage follows
+    the context's upload rule (bf16 for matrices on a bf16-precision context)."""
+    a = cuda.to_numpy(cuda.randn((257, 1001), 42, std=0.02))
+    b = cuda.to_numpy(cuda.randn((257, 1001), 42, std=0.02))
+    c = cuda.to_numpy(cuda.randn((257, 1001), 43, std=0.02))
+    assert np.array_equal(a, b) and not np.array_equal(a, c)
+    assert abs(float(a.mean())) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    assert abs(float(((a / 0.02) ** 4).mean()) - 3.0) < 0.1  # kurtosis of a normal
+    g = cuda.to_numpy(cuda.randn((64,), 0, std=0.0, mean=1.0))
+    assert (g == 1.0).all()
+    t = cuda_bf16.randn((64, 64), 7, std=0.02)
+    assert cuda_bf16.storage_of(t) == 2 and cuda_bf16.to_numpy(t).shape == (64, 64)
+    assert cuda.to_numpy(cuda.randn((0, 5), 1)).shape == (0, 5)
