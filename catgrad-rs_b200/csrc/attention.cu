@@ -234,6 +234,7 @@ int check(cg_ctx* c, const AttnArgs& a) {
 int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a) {
   CG_TRY(check(c, a));
   if (a.B == 0 || a.S == 0) return CG_OK;
+  if (c->opt_fa && attn_fa_supported(a)) return k_launch_attn_fa(c, a);
   switch (a.d) {
     case 64: return launch_prefill<64, 128, 2>(c, a);
     case 128: return launch_prefill<128, 128, 2>(c, a);

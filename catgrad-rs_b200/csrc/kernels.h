@@ -67,6 +67,11 @@ struct AttnArgs {
 // positions [0, pos0 + S).  Tensor-core flash kernel.
 int k_launch_attn_prefill(cg_ctx* c, const AttnArgs& a);
 
+// The same on tcgen05 / TMEM for head sizes 64 and 128 without soft-cap or window (attention_fa.cu);
+// k_launch_attn_prefill routes here by itself when the context allows it.
+bool attn_fa_supported(const AttnArgs& a);
+int k_launch_attn_fa(cg_ctx* c, const AttnArgs& a);
+
 struct AttnDecArgs {
   const float* qkv;              // [B, (nh + 2 nkv) d] f32: the fused projection of the new tokens
   const float* cos_t;            // rotary tables [Tmax, d/2]

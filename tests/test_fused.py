@@ -177,3 +177,30 @@ def test_randn_is_a_function_of_seed_and_index(cuda, cuda_bf16):
     t = cuda_bf16.randn((64, 64), 7, std=0.02)
     assert cuda_bf16.storage_of(t) == 2 and cuda_bf16.to_numpy(t).shape == (64, 64)
     assert cuda.to_numpy(cuda.randn((0, 5), 1)).shape == (0, 5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("b,nh,nkv,s,d", [(1, 4, 2, 128, 128), (2, 8, 2, 200, 64), (1, 4, 4, 385, 128), (1, 2, 1, 1000, 128),
+                                          (3, 4, 1, 64, 64)])
+def test_fused_attention_tcgen05(cuda, b, nh, nkv, s, d):
+    """The TMEM / tcgen05 prefill attention against the mma.sync kernel (itself checked against
+    the reference op stream above) and against a float64 numpy evaluation."""
+    q = synth.bf16_round(rnd((b, nh, s, d)))
+    k = synth.bf16_round(rnd((b, nkv, s, d)))
+    v = synth.bf16_round(rnd((b, nkv, s, d)))
+    args = [cuda.from_numpy(q), cuda.from_numpy(k), cuda.from_numpy(v)]
+    base = cuda.to_numpy(cuda.fused_attention(*args))
+    cuda.set_option("fa", 1)
+    try:
+        got = cuda.to_numpy(cuda.fused_attention(*args))
+    finally:
+        cuda.set_option("fa", 0)
+    rep = nh // nkv
+    kk, vv = np.repeat(k, rep, axis=1).astype(np.float64), np.repeat(v, rep, axis=1).astype(np.float64)
+    sc = np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), kk) / np.sqrt(d)
+    sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+    pr = np.exp(sc - sc.max(-1, keepdims=True))
+    want = np.einsum("bhqk,bhkd->bhqd", pr / pr.sum(-1, keepdims=True), vv)
+    np.testing.assert_allclose(got, want, rtol=0, atol=2e-2)
+    assert np.abs(got - want).mean() < 3e-3
+    np.testing.assert_allclose(got, base, rtol=0, atol=2e-2)
