@@ -164,6 +164,8 @@ def main():
     ap.add_argument("--decode", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="a 4-layer model of the same widths (profiling captures)")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="library switch (cg_set_option), e.g. fa=0; for experiments, not for the reported line")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and not args.small:
         args.warmup = 3
@@ -219,6 +221,9 @@ def main():
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     C = cg.CudaBackend(local, cg.PREC_BF16, stream=tstream.cuda_stream)
+    for kv in args.opt:
+        name, _, val = kv.partition("=")
+        C.set_option(name, int(val))
     if world > 1:
         importlib.import_module("catgrad-rs_b200.tp").init_comm(C, rank, world)
         mapped, why = C.peer_exchange()

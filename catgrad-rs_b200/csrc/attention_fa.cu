@@ -31,7 +31,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int FA_BQ = 128, FA_BK = 128;
+constexpr int FA_BQ = 128;
 
 struct FaArgs {
   __nv_bfloat16* out;  // [B * S, nh D]
@@ -54,22 +54,28 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t saddr, uint32_t chunk_
   return d;
 }
 
-template <int D>
-__global__ void __launch_bounds__(192, 1)
+template <int D, int FA_BK>
+__global__ void __launch_bounds__(192, FA_BK == 64 ? 2 : 1)
 k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
           const __grid_constant__ CUtensorMap map_v, FaArgs p) {
   constexpr int SUB = D / 64;                       // 64-wide sub-tiles along the head dimension
-  constexpr uint32_t BOX = 128 * 128;               // bytes of one [128 rows, 64 bf16] box
-  constexpr uint32_t Q_BYTES = SUB * BOX, KV_BYTES = SUB * BOX, P_BYTES = 2 * BOX;
+  constexpr uint32_t BOX = 128 * 128;               // bytes of one [128 rows, 64 bf16] box (Q, P)
+  constexpr uint32_t KBOX = FA_BK * 128;            // bytes of one [FA_BK keys, 64 bf16] box (K, V)
+  constexpr uint32_t Q_BYTES = SUB * BOX, KV_BYTES = SUB * KBOX, P_BYTES = (FA_BK / 64) * BOX;
   constexpr uint32_t S_COLS = FA_BK;                // one score buffer
   constexpr uint32_t O_COL = 2 * S_COLS;            // O_t after the two score buffers
-  constexpr uint32_t NCOLS = 512;
+  constexpr uint32_t NCOLS = 2 * S_COLS + D <= 256 ? 256 : 512;  // two CTAs per SM share 512 columns
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
+  if (FA_BK == 64 && base != raw) {
+    // the 64-key variant is sized without alignment slack (two CTAs must fit one SM)
+    if (threadIdx.x == 0) *p.err = DEV_TIMEOUT;
+    return;
+  }
   const uint32_t sq = base, sk = sq + Q_BYTES, sv = sk + 2 * KV_BYTES, sp = sv + 2 * KV_BYTES;
   const uint32_t bars = sp + P_BYTES;
   uint8_t* gen = smem_raw + (base - raw);
@@ -135,18 +141,18 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           if (!ok) break;
         }
         mbar_expect_tx(b_k_full + 8 * buf, KV_BYTES);
-        for (int s = 0; s < SUB; ++s) tma_load_2d(sk + buf * KV_BYTES + s * BOX, &map_k, s * 64, row, b_k_full + 8 * buf);
+        for (int s = 0; s < SUB; ++s) tma_load_2d(sk + buf * KV_BYTES + s * KBOX, &map_k, s * 64, row, b_k_full + 8 * buf);
         if (j >= 2) {
           ok = mbar_wait(b_v_empty + 8 * buf, ph ^ 1u, cta_abort, p.err);
           if (!ok) break;
         }
         mbar_expect_tx(b_v_full + 8 * buf, KV_BYTES);
-        for (int s = 0; s < SUB; ++s) tma_load_2d(sv + buf * KV_BYTES + s * BOX, &map_v, s * 64, row, b_v_full + 8 * buf);
+        for (int s = 0; s < SUB; ++s) tma_load_2d(sv + buf * KV_BYTES + s * KBOX, &map_v, s * 64, row, b_v_full + 8 * buf);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(FA_BK);              // 128 x 128, both operands k-major
+      constexpr uint32_t idesc_s = umma_idesc(FA_BK);              // 128 x FA_BK, both operands k-major
       constexpr uint32_t idesc_o = umma_idesc(D) | (1u << 16);     // 128 x D, B operand MN-major
       bool ok = mbar_wait(b_q_full, 0, cta_abort, p.err);
       // S_j = Q K_j^T into score buffer j & 1
@@ -157,8 +163,10 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < D / UMMA_K; ++kk) {
-          const uint32_t off = (uint32_t)(kk / 4) * BOX + (uint32_t)(kk % 4) * 32u;
-          umma_bf16(tmem_base + buf * S_COLS, umma_desc(sq + off), umma_desc(sk + buf * KV_BYTES + off), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t offq = (uint32_t)(kk / 4) * BOX + (uint32_t)(kk % 4) * 32u;
+          const uint32_t offk = (uint32_t)(kk / 4) * KBOX + (uint32_t)(kk % 4) * 32u;
+          umma_bf16(tmem_base + buf * S_COLS, umma_desc(sq + offq), umma_desc(sk + buf * KV_BYTES + offk), idesc_s,
+                    kk > 0 ? 1u : 0u);
         }
         umma_commit(b_s_full + 8 * buf);
         umma_commit(b_k_empty + 8 * buf);
@@ -174,7 +182,7 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
 #pragma unroll
         for (int kk = 0; kk < FA_BK / UMMA_K; ++kk) {
           const uint64_t da = umma_desc(sp + (uint32_t)(kk / 4) * BOX + (uint32_t)(kk % 4) * 32u);
-          const uint64_t db = umma_desc_mn(sv + buf * KV_BYTES + (uint32_t)kk * (UMMA_K * 128u), BOX);
+          const uint64_t db = umma_desc_mn(sv + buf * KV_BYTES + (uint32_t)kk * (UMMA_K * 128u), KBOX);
           umma_bf16(tmem_base + O_COL, da, db, idesc_o, kk > 0 ? 1u : 0u);
         }
         umma_commit(b_o_full);
@@ -302,18 +310,19 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   }
 }
 
-template <int D>
+template <int D, int FA_BK>
 int launch_fa(cg_ctx* c, const AttnArgs& a) {
-  constexpr size_t smem = (size_t)(D / 64) * 128 * 128 * 5 + 2 * 128 * 128 + 1024 + 256;
+  constexpr size_t smem =
+      (size_t)(D / 64) * (128 + 4 * FA_BK) * 128 + (size_t)(FA_BK / 64) * 128 * 128 + (FA_BK == 64 ? 0 : 1024) + 160;
   static bool configured = false;
   if (!configured) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_attn_fa<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_attn_fa<D, FA_BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   CUtensorMap mq, mk, mv;
   CG_TRY(make_map(c, &mq, a.q, a.B * a.S, (int64_t)a.nh * D, (int64_t)a.nh * D, 128));
-  CG_TRY(make_map(c, &mk, a.k_cache, a.B * a.nkv * a.Tmax, D, D, 128));
-  CG_TRY(make_map(c, &mv, a.v_cache, a.B * a.nkv * a.Tmax, D, D, 128));
+  CG_TRY(make_map(c, &mk, a.k_cache, a.B * a.nkv * a.Tmax, D, D, FA_BK));
+  CG_TRY(make_map(c, &mv, a.v_cache, a.B * a.nkv * a.Tmax, D, D, FA_BK));
   FaArgs p;
   p.out = a.out;
   p.S = a.S; p.pos0 = a.pos0; p.Tmax = a.Tmax;
@@ -321,7 +330,7 @@ int launch_fa(cg_ctx* c, const AttnArgs& a) {
   p.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
   p.err = c->core->dev_err;
   dim3 grid((unsigned)((a.S + FA_BQ - 1) / FA_BQ), (unsigned)a.nh, (unsigned)a.B);
-  CG_CUDA(c, launch_kernel(c, k_attn_fa<D>, grid, dim3(192), smem, 1, mq, mk, mv, p));
+  CG_CUDA(c, launch_kernel(c, k_attn_fa<D, FA_BK>, grid, dim3(192), smem, 1, mq, mk, mv, p));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -336,8 +345,9 @@ bool attn_fa_supported(const AttnArgs& a) {
 
 int k_launch_attn_fa(cg_ctx* c, const AttnArgs& a) {
   if (a.B == 0 || a.S == 0) return CG_OK;
-  if (a.d == 64) return launch_fa<64>(c, a);
-  return launch_fa<128>(c, a);
+  const bool k64 = c->opt_fa == 2;  // 64-key tiles: two CTAs per SM
+  if (a.d == 64) return k64 ? launch_fa<64, 64>(c, a) : launch_fa<64, 128>(c, a);
+  return k64 ? launch_fa<128, 64>(c, a) : launch_fa<128, 128>(c, a);
 }
 
 }  // namespace cg

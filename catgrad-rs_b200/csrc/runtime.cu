@@ -275,7 +275,7 @@ int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
   if (!strcmp(name, "gemm")) { c->opt_gemm = (int)value; return CG_OK; }
   if (!strcmp(name, "pdl")) { c->opt_pdl = value != 0; return CG_OK; }
   if (!strcmp(name, "peer")) { c->opt_peer = value != 0; return CG_OK; }
-  if (!strcmp(name, "fa")) { c->opt_fa = value != 0; return CG_OK; }
+  if (!strcmp(name, "fa")) { c->opt_fa = (int)value; return CG_OK; }
   if (!strcmp(name, "handover")) { c->opt_handover = value != 0; return CG_OK; }
   if (!strcmp(name, "persistent")) { c->opt_persistent = value != 0; return CG_OK; }
   return fail(c, CG_ERR_INVALID, std::string("unknown option ") + name);

@@ -182,19 +182,21 @@ def test_randn_is_a_function_of_seed_and_index(cuda, cuda_bf16):
 @pytest.mark.gpu
 @pytest.mark.parametrize("b,nh,nkv,s,d", [(1, 4, 2, 128, 128), (2, 8, 2, 200, 64), (1, 4, 4, 385, 128), (1, 2, 1, 1000, 128),
                                           (3, 4, 1, 64, 64)])
-def test_fused_attention_tcgen05(cuda, b, nh, nkv, s, d):
+@pytest.mark.parametrize("variant", [1, 2], ids=["keys128", "keys64"])
+def test_fused_attention_tcgen05(cuda, b, nh, nkv, s, d, variant):
     """The TMEM / tcgen05 prefill attention against the mma.sync kernel (itself checked against
     the reference op stream above) and against a float64 numpy evaluation."""
     q = synth.bf16_round(rnd((b, nh, s, d)))
     k = synth.bf16_round(rnd((b, nkv, s, d)))
     v = synth.bf16_round(rnd((b, nkv, s, d)))
     args = [cuda.from_numpy(q), cuda.from_numpy(k), cuda.from_numpy(v)]
+    cuda.set_option("fa", 0)
     base = cuda.to_numpy(cuda.fused_attention(*args))
-    cuda.set_option("fa", 1)
+    cuda.set_option("fa", variant)
     try:
         got = cuda.to_numpy(cuda.fused_attention(*args))
     finally:
-        cuda.set_option("fa", 0)
+        cuda.set_option("fa", 1)
     rep = nh // nkv
     kk, vv = np.repeat(k, rep, axis=1).astype(np.float64), np.repeat(v, rep, axis=1).astype(np.float64)
     sc = np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), kk) / np.sqrt(d)
