@@ -54,6 +54,26 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t saddr, uint32_t chunk_
   return d;
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 consecutive TMEM columns of this thread's lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]),
+        "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]),
+        "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
 template <int D, int FA_BK>
 __global__ void __launch_bounds__(192, FA_BK == 64 ? 2 : 1)
 k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -212,57 +232,76 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       ok = mbar_wait(b_s_full + 8 * buf, ph, cta_abort, p.err);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int64_t k0 = (int64_t)j * FA_BK;
-      const bool diag = k0 + FA_BK - 1 > p.pos0 + q0;  // some key of the tile may be masked for some row
-      // pass 1: row maximum of the visible scores
+      const int k0 = j * FA_BK;
+      // a key column c of this tile is visible to this row iff c <= lim (causal mask)
+      const int64_t lim64 = qpos - k0;
+      const int lim = lim64 > FA_BK ? FA_BK : (lim64 < -1 ? -1 : (int)lim64);
+      const bool diag = (int64_t)k0 + FA_BK - 1 > p.pos0 + q0;  // uniform: some key may be masked for some row
+      const uint32_t s_addr = lane_base + buf * S_COLS;
+      constexpr int NCH = FA_BK / 32;
+      uint32_t va[32], vb[32];
+      // pass 1: row maximum of the visible scores.  The loads are double-buffered: chunk c+1 is
+      // in flight while chunk c is reduced.
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < FA_BK; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_base + buf * S_COLS + (uint32_t)c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      tmem_ld32(s_addr, va);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float s = __uint_as_float(v[i]);
-          mx = (!diag || k0 + c0 + i <= qpos) ? fmaxf(mx, s) : mx;
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
+        if (c + 1 < NCH) tmem_ld32(s_addr + (uint32_t)(c + 1) * 32u, nxt);
+        if (!diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
+        } else {
+          const int rel = lim - c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = i <= rel ? fmaxf(mx, __uint_as_float(cur[i])) : mx;
         }
+        if (c + 1 < NCH) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
       const float m_new = fmaxf(m, mx);
       const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = exp2f((m - m_safe) * p.scale_log2e);  // 0 while m is -inf
+      const float corr = fast_exp2((m - m_safe) * p.scale_log2e);  // 0 while m is -inf
+      const float mc = m_safe * p.scale_log2e;
       // the previous tile's P must have been consumed before it is overwritten
       if (j >= 1) {
         ok = mbar_wait(b_p_empty, ((uint32_t)j & 1u) ^ 1u, cta_abort, p.err);
         if (!ok) break;
       }
-      // pass 2: p = exp2((s - m) * scale * log2 e), row sum, bf16 P into the swizzled tile
+      // pass 2: p = exp2(s * scale * log2 e - m * scale * log2 e), row sum, bf16 P into the swizzled tile
       float ls = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < FA_BK; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_base + buf * S_COLS + (uint32_t)c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        uint32_t pk[8];
+      tmem_ld32(s_addr, va);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float e0 = exp2f((__uint_as_float(v[i]) - m_safe) * p.scale_log2e);
-          float e1 = exp2f((__uint_as_float(v[i + 1]) - m_safe) * p.scale_log2e);
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
+        if (c + 1 < NCH) tmem_ld32(s_addr + (uint32_t)(c + 1) * 32u, nxt);
+        const int rel = lim - c * 32;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = fast_exp2(fmaf(__uint_as_float(cur[i]), p.scale_log2e, -mc));
+          float e1 = fast_exp2(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2e, -mc));
           if (diag) {
-            e0 = k0 + c0 + i <= qpos ? e0 : 0.f;
-            e1 = k0 + c0 + i + 1 <= qpos ? e1 : 0.f;
+            e0 = i <= rel ? e0 : 0.f;
+            e1 = i + 1 <= rel ? e1 : 0.f;
           }
-          // the sum uses the rounded values the MMA will see
+          ls += e0 + e1;
           const __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-          ls += __low2float(pr) + __high2float(pr);
           pk[i / 2] = *(const uint32_t*)&pr;
         }
-        // two 16-byte chunks of row r: chunk index ch = c0 / 8 (+1); sub-tile ch / 8, position (ch % 8) ^ (r % 8)
-        const int ch = c0 / 8;
-        const uint32_t rowb = sp + (uint32_t)(ch / 8) * BOX + (uint32_t)r * 128u;
-        const uint32_t a0 = rowb + (uint32_t)(((ch % 8) ^ (r & 7)) * 16);
-        const uint32_t a1 = rowb + (uint32_t)((((ch + 1) % 8) ^ (r & 7)) * 16);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]) : "memory");
+        // four 16-byte chunks of row r: chunk index ch = 4 c + t; sub-tile ch / 8, position (ch % 8) ^ (r % 8)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int ch = 4 * c + t;
+          const uint32_t a = sp + (uint32_t)(ch / 8) * BOX + (uint32_t)r * 128u + (uint32_t)(((ch % 8) ^ (r & 7)) * 16);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pk[4 * t]), "r"(pk[4 * t + 1]), "r"(pk[4 * t + 2]),
+                       "r"(pk[4 * t + 3])
+                       : "memory");
+        }
+        if (c + 1 < NCH) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
       // S buffer free for the tile after next; P visible to the tensor core
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -271,17 +310,20 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_p_full) : "memory");
       l = l * corr + ls;
       m = m_new;
-      // fold O_t = P V into the running output
+      // fold O_t = P V into the running output (same double-buffered loads)
       ok = mbar_wait(b_o_full, (uint32_t)j & 1u, cta_abort, p.err);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      tmem_ld32(lane_base + O_COL, va);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_base + O_COL + (uint32_t)c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
+        if (c + 1 < D / 32) tmem_ld32(lane_base + O_COL + (uint32_t)(c + 1) * 32u, nxt);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[c0 + i] = o[c0 + i] * corr + __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(cur[i]));
+        if (c + 1 < D / 32) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(b_o_empty) : "memory");
