@@ -756,7 +756,7 @@ int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** l
   CG_TRY(set_state(D, 0, 0));
   D->B = B;
   // the prompt is processed in position chunks so the workspace stays bounded
-  const int64_t chunk_tokens = 8192;
+  const int64_t chunk_tokens = c->opt_prefill_chunk;
   int64_t Sc = std::max<int64_t>(1, chunk_tokens / B);
   if (Sc > 64) Sc = Sc / 64 * 64;
   Sc = std::min(Sc, S);

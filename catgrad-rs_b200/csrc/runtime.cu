@@ -276,6 +276,11 @@ int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
   if (!strcmp(name, "pdl")) { c->opt_pdl = value != 0; return CG_OK; }
   if (!strcmp(name, "peer")) { c->opt_peer = value != 0; return CG_OK; }
   if (!strcmp(name, "fa")) { c->opt_fa = (int)value; return CG_OK; }
+  if (!strcmp(name, "prefill_chunk")) {
+    if (value < 64 || value > (1 << 20)) return fail(c, CG_ERR_INVALID, "prefill_chunk out of range");
+    c->opt_prefill_chunk = (int)value;
+    return CG_OK;
+  }
   if (!strcmp(name, "handover")) { c->opt_handover = value != 0; return CG_OK; }
   if (!strcmp(name, "persistent")) { c->opt_persistent = value != 0; return CG_OK; }
   return fail(c, CG_ERR_INVALID, std::string("unknown option ") + name);

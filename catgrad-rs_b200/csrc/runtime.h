@@ -85,6 +85,7 @@ struct cg_ctx {
   int opt_persistent = 1; // large GEMMs take the persistent double-buffered kernel
   int opt_handover = 1;   // decode steps: residual GEMMs prepare the next norm, the next GEMM applies 1 / rms
   int opt_fa = 1;         // prefill attention on tcgen05 (attention_fa.cu) where it applies
+  int opt_prefill_chunk = 8192;  // tokens per prefill chunk (bounds the decoder's workspace)
   int opt_peer = 1;       // small all-reduces over mapped peer memory instead of NCCL (when available)
   bool trace_on = false;  // record a device timeline of the decode GEMM launches
   int64_t trace_next = 0;
