@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(BQ * 2, D <= 64 ? 2 : 1) k_attn_prefill(AttnAr
 template <int D, int BQ, int NBUF>
 int launch_prefill(cg_ctx* c, const AttnArgs& a) {
   constexpr size_t smem = (size_t)(BQ + 2 * NBUF * 64) * (D + 8) * 2;
-  static bool configured = false;
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured && smem > 48 * 1024) {
     CG_CUDA(c, cudaFuncSetAttribute(k_attn_prefill<D, BQ, NBUF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;

@@ -356,7 +356,8 @@ template <int D, int FA_BK>
 int launch_fa(cg_ctx* c, const AttnArgs& a) {
   constexpr size_t smem =
       (size_t)(D / 64) * (128 + 4 * FA_BK) * 128 + (size_t)(FA_BK / 64) * 128 * 128 + (FA_BK == 64 ? 0 : 1024) + 160;
-  static bool configured = false;
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_attn_fa<D, FA_BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;

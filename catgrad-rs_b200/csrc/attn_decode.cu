@@ -346,12 +346,14 @@ template <int D>
 int launch(cg_ctx* c, const AttnDecArgs& a) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(16 * LD + 8 * 32 * LD) * 2 + (size_t)(2 * D + 8 * MAX_REP + 16) * 4;
-  static bool configured = false;
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured && smem > 48 * 1024) {
     CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  static bool wide = false;
+  static PerDeviceFlag wide_on;
+  bool& wide = wide_on.at(c->core->device);
   if (!wide && a.splits > 8) {
     CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     wide = true;

@@ -67,7 +67,7 @@ struct cg_decoder {
   int64_t B = 0, pos = 0, generated = 0;
   // workspace (sized for `cap` tokens)
   int64_t cap = 0;
-  cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *gu = nullptr, *hact = nullptr,
+  cg_tensor *x = nullptr, *xn = nullptr, *qkvb = nullptr, *q = nullptr, *att = nullptr, *hact = nullptr,
             *tmp = nullptr, *xl = nullptr, *splitk = nullptr, *best = nullptr;
   // mixture-of-experts scratch, sized for cap * top_k pairs
   cg_tensor *m_ids = nullptr, *m_wts = nullptr, *m_pos = nullptr, *m_tiles = nullptr, *m_xg = nullptr, *m_h = nullptr,
@@ -133,7 +133,7 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   if (M <= D->cap) return CG_OK;
   cg_ctx* c = D->c;
   if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }  // it holds the old buffers
-  drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact); drop(D->tmp);
+  drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->hact); drop(D->tmp);
   const int64_t H = D->H;
   int64_t s2[2];
   s2[0] = M; s2[1] = H;
@@ -145,8 +145,6 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   s2[1] = (int64_t)D->nh * D->d;
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->q));
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->att));
-  s2[1] = 2 * (int64_t)D->F;
-  CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->gu));
   s2[1] = D->F;
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->hact));
   if (D->cfg.n_experts > 0) {
@@ -556,7 +554,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   }
   if (D->head != D->embed) drop(D->head);
   drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
-  drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->gu); drop(D->hact);
+  drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->hact);
   drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best); drop(D->ss);
   drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
   drop(D->m_xs3); drop(D->m_logits);
@@ -853,8 +851,8 @@ int32_t cg_decoder_time_gemms(cg_decoder* D, int32_t batch, int32_t iters, float
       st = gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0);
       if (st == CG_OK) st = gemm(D, D->att, M, L.w_o, D->tmp->data(), nullptr, 0);
       if (L.moe) continue;  // the expert GEMMs depend on the routing: not part of this sweep
-      if (st == CG_OK) st = small ? gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 1, true)
-                                  : gemm(D, D->xn, M, L.w_gu, D->gu->data(), nullptr, 0);
+      if (st == CG_OK) st = gemm(D, D->xn, M, L.w_gu, D->hact->data(), nullptr, 1, true);
+      (void)small;
       if (st == CG_OK) st = gemm(D, D->hact, M, L.w_down, D->tmp->data(), nullptr, 0);
     }
     if (st == CG_OK) st = gemm(D, D->xl, M, D->head, D->logits->data(), nullptr, 0);

@@ -324,7 +324,8 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 
 template <int TN>
 int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const DecArgs& a, dim3 grid, size_t smem) {
-  static size_t configured = 0;  // largest dynamic shared memory size set so far
+  static PerDeviceSize configured_on;
+  size_t& configured = configured_on.at(c->core->device);
   if (smem > configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));

@@ -306,7 +306,8 @@ __global__ void k_splitk_reduce(const float* partial, int splits, int64_t M, int
 template <int TN, int STAGES, int MINB, int ACC2 = 0>
 int launch(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, dim3 grid) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES * (1 + ACC2) + TN * BK * 2) + 1024 + 16 * STAGES + 64;
-  static bool configured = false;  // per instantiation; the attribute is per function and device-wide
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tc<TN, STAGES, MINB, ACC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;

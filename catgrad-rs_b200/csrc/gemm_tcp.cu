@@ -260,7 +260,8 @@ k_gemm_tcp(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 template <int TN, int PAIR, int STAGES, int GROUPED>
 int launch_tcp(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, const TcpArgs& a, int ctas) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES * (1 + PAIR) + TN * BK * 2) + 1024 + 16 * STAGES + 64;
-  static bool configured = false;
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tcp<TN, PAIR, STAGES, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;

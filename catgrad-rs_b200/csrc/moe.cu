@@ -464,7 +464,8 @@ template <int TN, int DUAL, int STAGES, int MINB>
 int launch_moe_gemm(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, const MoeGemmArgs& a,
                     dim3 grid) {
   constexpr size_t smem = (size_t)STAGES * (A_BYTES * (DUAL ? 2 : 1) + TN * BK * 2) + 1024 + 16 * STAGES + 64;
-  static bool configured = false;
+  static PerDeviceFlag configured_on;
+  bool& configured = configured_on.at(c->core->device);
   if (!configured) {
     CG_CUDA(c, cudaFuncSetAttribute(k_moe_gemm<TN, DUAL, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
@@ -515,7 +516,8 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
     CG_LAUNCHED(c);
   } else {
     const size_t smem = (size_t)(a.H + a.E) * 4;
-    static size_t configured = 0;
+    static PerDeviceSize configured_on;
+  size_t& configured = configured_on.at(c->core->device);
     if (smem > 48 * 1024 && smem > configured) {
       CG_CUDA(c, cudaFuncSetAttribute(k_moe_route, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = smem;

@@ -149,6 +149,17 @@ int cuda_fail(cg_ctx* c, cudaError_t e, const char* what);
     if (st__ != CG_OK) return st__; \
   } while (0)
 
+// Function attributes (dynamic shared memory limit, cluster size) are set per device: call sites
+// keep one of these per function so that every GPU a process uses gets configured once.
+struct PerDeviceFlag {
+  bool done[64] = {};
+  bool& at(int device) { return done[device & 63]; }
+};
+struct PerDeviceSize {
+  size_t v[64] = {};
+  size_t& at(int device) { return v[device & 63]; }
+};
+
 // New contiguous tensor with fresh storage.
 int new_tensor(cg_ctx* c, int tag, int storage, const int64_t* dims, int rank, cg_tensor** out);
 // New handle sharing t's buffer (same view); caller edits dims/strides/offset.

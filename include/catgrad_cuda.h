@@ -252,11 +252,16 @@ typedef struct cg_decoder_config {
   float final_softcap;
   int32_t sliding_window;   /* 0 = none */
   int32_t window_every;     /* layers with (i % window_every) != window_every-1 use the window */
-  int32_t n_experts;        /* 0 = dense FFN */
-  int32_t top_k;
-  int32_t moe_ffn;
-  int32_t norm_topk;
-  /* tensor parallelism: this rank's place; 1 rank = no communication */
+  /* mixture of experts (qwen3.rs:64-133): a layer whose checkpoint carries a router
+   * ("...mlp.gate.weight" [n_experts, hidden]) and stacked experts
+   * ("...mlp.experts.{gate,up,down}_proj.weight") runs the expert block instead of the dense FFN */
+  int32_t n_experts;        /* 0 = dense FFN everywhere; at most 1024 */
+  int32_t top_k;            /* experts per token, 1..32 */
+  int32_t moe_ffn;          /* width of one expert */
+  int32_t norm_topk;        /* renormalise the top-k probabilities to sum 1 */
+  /* tensor parallelism: this rank's place; 1 rank = no communication.  Heads, dense FFN columns
+   * and the vocabulary are split over the ranks (fewer kv heads than ranks: kv heads are
+   * replicated), whole experts are owned by ranks. */
   int32_t tp_rank;
   int32_t tp_world;
 } cg_decoder_config;
