@@ -176,7 +176,7 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
 
 // The expert block of layer L on M tokens; under tensor parallelism every rank owns whole
 // experts and the partial sums meet in the all-reduce of the residual stream.
-int moe_block(cg_decoder* D, Layer& L, int64_t M) {
+int moe_block(cg_decoder* D, Layer& L, int64_t M, bool push = false) {
   const cg_decoder_config& cfg = D->cfg;
   const int64_t P = M * cfg.top_k;
   MoeArgs a;
@@ -207,6 +207,13 @@ int moe_block(cg_decoder* D, Layer& L, int64_t M) {
   a.w.h = (__nv_bfloat16*)D->m_h->data();
   a.w.y = (float*)D->m_y->data();
   (void)P;
+  PeerPush px;
+  if (push) {
+    // decode under tensor parallelism: no collective call (see project_add)
+    px = peer_push_of(D->c->xchg);
+    a.push = &px;
+    return moe_ffn(D->c, a);
+  }
   CG_TRY(moe_ffn(D->c, a));
   return all_reduce_f32(D, (float*)D->x->data(), M * D->H);
 }
@@ -301,7 +308,7 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
 bool use_push(cg_decoder* D, int64_t M, int64_t S) {
   const cg_decoder_config& cfg = D->cfg;
   return cfg.tp_world > 1 && D->c->xchg.ok && D->c->opt_peer && S == 1 && small_m(M, D->H) && !cfg.post_norms &&
-         cfg.n_experts == 0 && M * D->H <= D->c->xchg.max_elems;
+         M * D->H <= D->c->xchg.max_elems;
 }
 
 // All layers for M = B * S new tokens at positions [pos0, pos0 + S); x holds the embeddings.
@@ -382,6 +389,11 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     }
     if (!(handover && !L.moe))
       CG_TRY(project_add(D, D->att, M, L.w_o, L.ln_post_attn, push, cfg.post_norms && !L.moe ? L.ln_pre_ffn : nullptr));
+    if (push && L.moe) {
+      CG_TRY(moe_block(D, L, M, true));
+      D->pending_reduce = true;
+      continue;
+    }
     if (push) {
       CG_TRY(k_launch_rmsnorm_reduce(c, px, (float*)D->x->data(), D->H, (const float*)L.ln_pre_ffn->data(), cfg.rms_eps,
                                      cfg.norm_plus_one, M, D->H, D->xn->data(), 1));

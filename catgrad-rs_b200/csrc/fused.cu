@@ -4,6 +4,7 @@
 // Rows are reduced with warp shuffles; loads are 128-bit where the row length allows.
 #include "act.cuh"
 #include "kernels.h"
+#include "peer.cuh"
 
 #include <algorithm>
 
@@ -315,23 +316,6 @@ __global__ void k_argmax_finish(unsigned long long* best, int64_t B, uint32_t* t
   }
 }
 
-// Bounded wait until a flag written by another GPU reaches `want`; on expiry raises the
-// context's error word and gives up (the caller carries on with whatever data is there).
-__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t want, int32_t* err) {
-  unsigned long long t0 = 0;
-  for (uint32_t it = 0;; ++it) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-    if (v == want) return true;
-    if ((it & 0xFF) == 0xFF) {
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) { *err = DEV_TIMEOUT; return false; }
-    }
-  }
-}
-
 // One block per row: x[m, :] += addends of all ranks (rank order), then the row's RMSNorm.
 template <int OUT_BF16>
 __global__ void k_rmsnorm_reduce(PeerPush px, float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t H,
@@ -341,7 +325,7 @@ __global__ void k_rmsnorm_reduce(PeerPush px, float* x, int64_t ldx, const float
   __shared__ float sh[32];
   const uint32_t e = *(volatile uint32_t*)px.epoch;  // the reduction the preceding kernel pushed
   const uint32_t par = e & 1u;
-  if ((int)threadIdx.x < px.world) wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
+  if ((int)threadIdx.x < px.world) peer_wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
   __syncthreads();
   const int64_t m = blockIdx.x;
   float* row = x + m * ldx;
@@ -383,7 +367,7 @@ __global__ void k_argmax_finish_tp(PeerPush px, unsigned long long* best, int64_
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(px.flags[r] + par * px.world + px.rank), "r"(e) : "memory");
     *(volatile uint32_t*)px.epoch = e;
   }
-  if ((int)threadIdx.x < px.world) wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
+  if ((int)threadIdx.x < px.world) peer_wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
   __syncthreads();
   const int64_t count = *count_dev;
   for (int64_t b = threadIdx.x; b < B; b += blockDim.x) {

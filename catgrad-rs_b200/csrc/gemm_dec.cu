@@ -22,6 +22,7 @@
 
 #include "act.cuh"
 #include "kernels.h"
+#include "peer.cuh"
 #include "tc_common.cuh"
 
 namespace cg {
@@ -226,7 +227,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   // the reduction this kernel contributes to: one more than the last one this rank pushed
   // (stable until this kernel's last CTA has seen every other CTA finish)
   uint32_t parity = 0;
-  if (p.out_mode == 3 && warp >= 2) parity = (*(volatile uint32_t*)p.push.epoch + 1u) & 1u;
+  if (p.out_mode == 3 && warp >= 2) parity = peer_push_parity(p.push);
   if (warp >= 2 && acc_ok) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -304,21 +305,8 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
   }
-  if (p.out_mode == 3 && tid == 0) {
-    // every thread's pushes precede the barrier above; the fence orders them (system wide)
-    // before this CTA's ticket, and the CTA that draws the last ticket raises the flags
-    __threadfence_system();
-    const unsigned t = atomicAdd(p.push.ticket, 1u);
-    if (t == (unsigned)p.total_ctas - 1u) {
-      *p.push.ticket = 0u;
-      const uint32_t e = *(volatile uint32_t*)p.push.epoch + 1u;
-      __threadfence_system();
-      for (int r = 0; r < p.push.world; ++r)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push.flags[r] + (e & 1u) * p.push.world + p.push.rank), "r"(e)
-                     : "memory");
-      *(volatile uint32_t*)p.push.epoch = e;
-    }
-  }
+  // every thread's pushes precede the barrier above
+  if (p.out_mode == 3 && tid == 0) peer_push_done(p.push, (unsigned)p.total_ctas);
   if (tid == 0) trace_max(p.trace, 3);
 }
 

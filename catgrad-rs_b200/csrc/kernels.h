@@ -192,6 +192,8 @@ struct MoeArgs {
   int H, E, k, Fe, norm_topk, act;
   int e_lo, El;               // this rank owns experts [e_lo, e_lo + El)
   int add_residual;           // 1: out = x + expert sum; 0: out = this rank's expert sum only
+  const PeerPush* push = nullptr;  // tensor-parallel decode: x (= out) first receives the addends pushed by the
+                              // preceding row-parallel GEMM, and the expert sum is pushed as the next addend
   int64_t M;
   __nv_bfloat16* xn;          // [M, H] scratch: the normalised rows
   MoeWork w;

@@ -24,6 +24,7 @@
 
 #include "act.cuh"
 #include "kernels.h"
+#include "peer.cuh"
 #include "tc_common.cuh"
 
 namespace cg {
@@ -123,15 +124,32 @@ __global__ void k_moe_route(const float* x, const float* gamma, float eps, int p
 // v to within an ulp of f32 -- and multiplied with the (bf16) router matrix repeated three
 // times along k.  Every product is exact in f32, only the accumulation order differs from
 // the reference's.  One block per token; also writes the plain bf16 row the experts read.
-__global__ void k_moe_norm_split(const float* x, const float* gamma, float eps, int plus_one, int H, __nv_bfloat16* xn,
-                                 __nv_bfloat16* xs3) {
+// REDUCE: the rows first receive the addends the ranks pushed for the latest reduction (the
+// attention output projection under tensor parallelism), as k_rmsnorm_reduce does.
+template <int REDUCE>
+__global__ void k_moe_norm_split(float* x, const float* gamma, float eps, int plus_one, int H, __nv_bfloat16* xn,
+                                 __nv_bfloat16* xs3, PeerPush px, int32_t* err) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float red[32];
   const int64_t m = blockIdx.x;
-  const float* row = x + m * H;
+  float* row = x + m * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) ss += row[i] * row[i];
+  if (REDUCE) {
+    const uint32_t e = *(volatile uint32_t*)px.epoch;
+    const uint32_t par = e & 1u;
+    if ((int)threadIdx.x < px.world) peer_wait_flag(px.flags[px.rank] + par * px.world + threadIdx.x, e, err);
+    __syncthreads();
+    const float* slots = px.data[px.rank] + (int64_t)par * px.world * px.max_elems + m * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float acc = row[i];
+      for (int r = 0; r < px.world; ++r) acc += __ldcg(slots + (int64_t)r * px.max_elems + i);
+      row[i] = acc;  // read back below by this same thread
+      ss += acc * acc;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ss += row[i] * row[i];
+  }
   ss = block_sum_f(ss, red);
   const float rms = sqrtf(ss / (float)H + eps);
   __nv_bfloat16* o3 = xs3 + m * 3 * H;
@@ -278,10 +296,14 @@ __global__ void k_moe_gather(const __nv_bfloat16* xn, const int32_t* pos, int64_
 
 // out[t, :] = (add_residual ? x[t, :] : 0) + sum over slots s of wts[t, s] * y[pos[t k + s], :]
 // (out may be x itself)
+// PUSH: instead of writing `out`, every rank's exchange area receives this rank's expert sum as
+// its addend of the next reduction (no residual: the consumer adds the addends to x).
+template <int PUSH>
 __global__ void k_moe_combine(const float* y, const int32_t* pos, const float* wts, int64_t M, int k, int H, int add_residual,
-                              const float* x, float* out) {
+                              const float* x, float* out, PeerPush px) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t slot0 = PUSH ? ((int64_t)peer_push_parity(px) * px.world + px.rank) * px.max_elems : 0;
   const int per = H / 4;
   const int64_t total = M * per;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -295,11 +317,19 @@ __global__ void k_moe_combine(const float* y, const int32_t* pos, const float* w
       const float4 v = ((const float4*)(y + (int64_t)r * H))[j];
       acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
     }
+    if (PUSH) {
+      for (int r = 0; r < px.world; ++r) ((float4*)(px.data[r] + slot0 + t * H))[j] = acc;
+      continue;
+    }
     if (add_residual) {
       const float4 b = ((const float4*)(x + t * H))[j];
       acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
     }
     ((float4*)(out + t * H))[j] = acc;
+  }
+  if (PUSH) {
+    __syncthreads();
+    if (threadIdx.x == 0) peer_push_done(px, gridDim.x);
   }
 }
 
@@ -477,6 +507,20 @@ int launch_moe_gemm(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mu, con
 
 }  // namespace
 
+static int launch_combine(cg_ctx* c, const MoeArgs& a) {
+  const dim3 grid(grid_for(a.M * (a.H / 4), 256));
+  if (a.push) {
+    if (a.M * a.H > a.push->max_elems) return fail(c, CG_ERR_INVALID, "moe: rows do not fit the exchange area");
+    CG_CUDA(c, launch_kernel(c, k_moe_combine<1>, grid, dim3(256), 0, 1, (const float*)a.w.y, (const int32_t*)a.w.pos,
+                             (const float*)a.w.wts, a.M, a.k, a.H, 0, a.x, a.out, *a.push));
+  } else {
+    CG_CUDA(c, launch_kernel(c, k_moe_combine<0>, grid, dim3(256), 0, 1, (const float*)a.w.y, (const int32_t*)a.w.pos,
+                             (const float*)a.w.wts, a.M, a.k, a.H, a.add_residual, a.x, a.out, PeerPush{}));
+  }
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
 int moe_pick_tn(int64_t pairs, int experts) {
   const int64_t avg = (pairs + experts - 1) / std::max(1, experts);
   return avg <= 8 ? 16 : avg <= 20 ? 32 : avg <= 40 ? 64 : 128;
@@ -489,6 +533,7 @@ int64_t moe_max_tiles(int64_t pairs, int experts_local, int tn) {
 int moe_ffn(cg_ctx* c, const MoeArgs& a) {
   if (a.M == 0) return CG_OK;
   if (a.k < 1 || a.k > 32 || a.k > a.E) return fail(c, CG_ERR_UNSUPPORTED, "moe: experts per token must be in [1, 32]");
+  if (a.push && !a.router3) return fail(c, CG_ERR_INVALID, "moe: the pushed reduction needs the bf16 router path");
   if (a.E > 1024 || a.H % 8 || a.Fe % 8) return fail(c, CG_ERR_UNSUPPORTED, "moe: sizes must be multiples of 8, at most 1024 experts");
   const int64_t P = a.M * a.k;
   if (P > 2147483647ll / 4) return fail(c, CG_ERR_UNSUPPORTED, "moe: too many (token, expert) pairs");
@@ -497,8 +542,12 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
   if (max_tiles > 65535) return fail(c, CG_ERR_UNSUPPORTED, "moe: too many tiles");
 
   if (a.router3) {
-    CG_CUDA(c, launch_kernel(c, k_moe_norm_split, dim3((unsigned)a.M), dim3(256), 0, 1, a.x, a.gamma, a.eps, a.plus_one, a.H, a.xn,
-                             a.xs3));
+    if (a.push)
+      CG_CUDA(c, launch_kernel(c, k_moe_norm_split<1>, dim3((unsigned)a.M), dim3(256), 0, 1, a.out, a.gamma, a.eps, a.plus_one, a.H,
+                               a.xn, a.xs3, *a.push, c->core->dev_err));
+    else
+      CG_CUDA(c, launch_kernel(c, k_moe_norm_split<0>, dim3((unsigned)a.M), dim3(256), 0, 1, const_cast<float*>(a.x), a.gamma, a.eps,
+                               a.plus_one, a.H, a.xn, a.xs3, PeerPush{}, c->core->dev_err));
     CG_LAUNCHED(c);
     const int64_t K3 = 3 * (int64_t)a.H;
     if (gemm_dec_supported(a.M, K3)) {
@@ -553,10 +602,7 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
                             a.w.tile_rows, a.w.n_tiles, max_tiles));
     CG_TRY(gemm_tcp_grouped(c, a.w.h, P, a.w_down, nullptr, a.El, a.w.y, a.H, a.Fe, 0, 0, a.w.tile_expert, a.w.tile_row0,
                             a.w.tile_rows, a.w.n_tiles, max_tiles));
-    CG_CUDA(c, launch_kernel(c, k_moe_combine, dim3(grid_for(a.M * (a.H / 4), 256)), dim3(256), 0, 1, (const float*)a.w.y,
-                             (const int32_t*)a.w.pos, (const float*)a.w.wts, a.M, a.k, a.H, a.add_residual, a.x, a.out));
-    CG_LAUNCHED(c);
-    return CG_OK;
+    return launch_combine(c, a);
   }
   switch (tn) {
     case 16: CG_TRY((launch_moe_gemm<16, 1, 3, 2>(c, mw, mu, mx, g, grid))); break;
@@ -575,10 +621,7 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
     case 64: CG_TRY((launch_moe_gemm<64, 0, 4, 2>(c, mw, mw, mx, g, grid))); break;
     default: CG_TRY((launch_moe_gemm<128, 0, 6, 1>(c, mw, mw, mx, g, grid))); break;
   }
-  CG_CUDA(c, launch_kernel(c, k_moe_combine, dim3(grid_for(a.M * (a.H / 4), 256)), dim3(256), 0, 1, (const float*)a.w.y,
-                           (const int32_t*)a.w.pos, (const float*)a.w.wts, a.M, a.k, a.H, a.add_residual, a.x, a.out));
-  CG_LAUNCHED(c);
-  return CG_OK;
+  return launch_combine(c, a);
 }
 
 }  // namespace cg

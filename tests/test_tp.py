@@ -130,8 +130,8 @@ KVREP_CFG = ('cg.synth.ModelConfig("kvrep-gpu", 256, 512, 2, 4, 1, 1024, rope_th
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("peer,cfg_expr", [(1, DENSE_CFG), (0, DENSE_CFG), (0, MOE_CFG), (1, KVREP_CFG)],
-                         ids=["peer-push", "nccl", "experts", "kv-replicated"])
+@pytest.mark.parametrize("peer,cfg_expr", [(1, DENSE_CFG), (0, DENSE_CFG), (0, MOE_CFG), (1, MOE_CFG), (1, KVREP_CFG)],
+                         ids=["peer-push", "nccl", "experts-nccl", "experts-push", "kv-replicated"])
 def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer, cfg_expr):
     """peer=1: decode steps reduce over mapped peer memory (GEMM epilogue pushes, norm kernel
     sums); peer=0: NCCL all-reduce / all-gather.  Both must reproduce one GPU."""
