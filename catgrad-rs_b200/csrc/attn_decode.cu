@@ -374,7 +374,9 @@ int attn_dec_splits(int64_t Tmax, int64_t pairs) {
   // (16 slices -- a cluster size this GPU supports beyond the portable 8 -- were measured for
   // few (row, kv head) pairs with long contexts and were slower: 2.92 -> 3.15 ms per step on
   // the 256-wide heads of the Gemma shape.)
-  (void)pairs;
+  // many (row, kv head) pairs: fewer, longer slices, so that the fixed cost of a CTA (query
+  // preparation, merges) is spread over more keys; keep about four waves of CTAs
+  while (s > 1 && pairs * s > 4 * 3 * 148 && (int64_t)(s / 2) * 1024 >= Tmax / 4) s /= 2;
   return s;
 }
 
