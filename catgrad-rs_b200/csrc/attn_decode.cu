@@ -368,9 +368,13 @@ int launch(cg_ctx* c, const AttnDecArgs& a) {
 
 // context slices per (row, kv head): a power of two up to 8 (one portable cluster), about
 // 128 keys per slice at full context
-int attn_dec_splits(int64_t Tmax, int64_t pairs) {
+int attn_dec_splits(int64_t Tmax, int64_t pairs, int d) {
   int s = 1;
   while (s < 8 && (int64_t)s * 128 < Tmax) s *= 2;
+  // head size 256: a CTA needs 143 KB of shared memory, one CTA per SM, and a cluster of 8 such
+  // CTAs needs 8 free SMs in one GPC -- fewer clusters fit than there are SMs (measured: 128
+  // CTAs took two waves).  Clusters of 4 place freely.
+  if (d > 128 && s > 4) s = 4;
   // (16 slices -- a cluster size this GPU supports beyond the portable 8 -- were measured for
   // few (row, kv head) pairs with long contexts and were slower: 2.92 -> 3.15 ms per step on
   // the 256-wide heads of the Gemma shape.)

@@ -356,7 +356,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
       f.nh = D->nh; f.nkv = D->nkv; f.d = D->d;
       f.window = windowed ? cfg.sliding_window : 0;
       f.softcap = cfg.attn_softcap;
-      f.splits = attn_dec_splits(cfg.max_seq, B * D->nkv);
+      f.splits = attn_dec_splits(cfg.max_seq, B * D->nkv, D->d);
       CG_TRY(k_launch_attn_dec(c, f));
     } else {
     RopeStoreArgs r;

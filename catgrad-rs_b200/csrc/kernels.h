@@ -92,7 +92,7 @@ struct AttnDecArgs {
 };
 // Rope + cache append + attention + merge of one new token per row, in one launch.
 int k_launch_attn_dec(cg_ctx* c, const AttnDecArgs& a);
-int attn_dec_splits(int64_t Tmax, int64_t pairs);
+int attn_dec_splits(int64_t Tmax, int64_t pairs, int d);
 
 // tokens[b] = argmax over the vocabulary with the reference's tie rule (last index); optional
 // soft-cap applied to the logits in place first.  The logits are `parts` vocabulary slices of
