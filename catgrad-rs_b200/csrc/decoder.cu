@@ -902,16 +902,14 @@ int32_t cg_decoder_generate(cg_decoder* D, const uint32_t* prompt, int32_t batch
   CG_TRY(cg_ndarray_from_vec_u32(c, prompt, (int64_t)batch * seq, dims, 2, &tk));
   Hold htk(tk);
   CG_TRY(cg_decoder_prefill(D, tk, nullptr));
+  CG_TRY(cg_decoder_decode(D, n_decode, nullptr));
+  // The reference reads every step's token back before the next forward (main.rs:160) because
+  // its host loop feeds it in again; here the device feeds itself, so all steps are enqueued
+  // back to back and the token history [batch, 1 + n_decode] comes back in one strided copy.
   const int64_t ld = 1 + (int64_t)n_decode;
-  std::vector<uint32_t> step((size_t)batch);
-  for (int i = 0; i <= n_decode; ++i) {
-    if (i > 0) CG_TRY(cg_decoder_decode(D, 1, nullptr));
-    // like the reference's per-step to_vec: read this step's tokens back before going on
-    CG_CUDA(c, cudaMemcpyAsync(step.data(), D->cur->data(), (size_t)batch * 4, cudaMemcpyDeviceToHost, c->core->stream));
-    CG_TRY(cg_sync(c));
-    for (int b = 0; b < batch; ++b) out[b * ld + i] = step[b];
-  }
-  return CG_OK;
+  CG_CUDA(c, cudaMemcpy2DAsync(out, (size_t)ld * 4, D->history->data(), (size_t)D->cfg.max_seq * 4, (size_t)ld * 4, (size_t)batch,
+                               cudaMemcpyDeviceToHost, c->core->stream));
+  return cg_sync(c);
 }
 
 }  // extern "C"
