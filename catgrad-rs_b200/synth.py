@@ -36,7 +36,7 @@ class ModelConfig:
     norm_topk_prob: bool = False
     decoder_sparse_step: int = 1
     # gemma (catgrad-llm/src/models/gemma3.rs graph; the soft-caps and the window are the
-    # Gemma-2 additions of BASELINE config 3, composed from reference ops)
+    # Gemma-2 additions of the Gemma-2-2B benchmark shape, composed from reference ops)
     qk_norm: bool = False             # per-head q/k RMSNorm (qwen3 always, gemma3 yes, gemma-2 no)
     attn_logit_softcap: float = 0.0
     final_logit_softcap: float = 0.0
@@ -51,7 +51,7 @@ class ModelConfig:
         return self.head_dim
 
 
-# BASELINE configurations (shapes only; weights are synthetic)
+# benchmark configurations (shapes only; weights are synthetic)
 TINY_LLAMA = ModelConfig("tiny-llama-f32", 256, 688, 2, 4, 2, 32000, rms_norm_eps=1e-5, rope_theta=10000.0,
                          tie_word_embeddings=False, dtype="f32")
 LLAMA_32_1B = ModelConfig("llama-3.2-1b-shape", 2048, 8192, 16, 32, 8, 128256, rms_norm_eps=1e-5,

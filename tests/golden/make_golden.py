@@ -45,7 +45,7 @@ def top(logits, n=8):
 
 
 def tiny_llama(B):
-    """BASELINE configuration 1: prefill of 32 seeded ids, then 16 greedy decode steps."""
+    """The CPU-runnable benchmark configuration: prefill of 32 seeded ids, then 16 greedy decode steps."""
     cfg = synth.TINY_LLAMA
     params = {n: B.from_numpy(w) for n, w in synth.make_weights(cfg, 0)}
     prompt = synth.make_tokens(cfg, 1, 32, seed=1)[0]

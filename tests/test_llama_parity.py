@@ -1,7 +1,7 @@
 """Whole-model parity.  No reference test pins logits or greedy tokens ("parity unpinned"),
 so the checker is the CPU restatement running the reference's own op stream.
 
-* tiny Llama, f32 (BASELINE config 1): the same op stream on the CUDA backend — logits within
+* tiny Llama, f32 (the CPU-runnable benchmark configuration): the same op stream on the CUDA backend — logits within
   1e-4 relative of the checker, identical greedy tokens over prefill + 16 decode steps.
 * the fused, KV-cached decoder (bf16) on shrunken Llama shapes: logits within 2e-2 of the f32
   checker on the same bf16-rounded weights, tokens identical wherever the checker's own
