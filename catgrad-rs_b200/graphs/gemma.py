@@ -3,7 +3,7 @@ reference tree lacks (attention logit soft-cap, final logit soft-cap, sliding-wi
 composed from reference ops: cap * tanh(x / cap) with the stdlib's tanh
 (catgrad/src/stdlib/nn/mod.rs:138-144) and a second `lt` on the arange grids of
 `causal_mask` (catgrad-llm/src/helpers.rs:239-257).  With qk_norm=False, one rope base and the
-soft-caps/window set, this is the Gemma-2-shaped BASELINE configuration; with qk_norm=True and
+soft-caps/window set, this is the Gemma-2-shaped benchmark configuration; with qk_norm=True and
 no caps it is the reference's Gemma3 graph (single rope base)."""
 from __future__ import annotations
 
