@@ -284,7 +284,7 @@ int sm_count(cg_ctx* c) {
 
 bool gemm_tcp_wanted(int64_t M, int64_t N, int64_t K) {
   // enough 128 x 256 tiles that every SM gets at least two, and a k loop worth pipelining
-  return M >= 512 && ((M + 255) / 256) * ((N + BM - 1) / BM) >= 2 * 148 && K >= 4 * BK;
+  return M >= 512 && ((M + 255) / 256) * ((N + BM - 1) / BM) >= 200 && K >= 4 * BK;
 }
 
 int gemm_tcp(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, int64_t w_rows, void* out,

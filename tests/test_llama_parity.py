@@ -154,3 +154,30 @@ def test_batch_rows_are_independent(cuda_bf16):
         dec.reset()
         np.testing.assert_array_equal(dec.generate(prompt[b:b + 1], 8)[0], batched[b])
     dec.close()
+
+
+@pytest.mark.parametrize("cfg", [SMALL, SMALL_D128], ids=lambda c: c.name)
+def test_chunked_prefill_equals_one_chunk_and_kernel_variants_agree(cuda_bf16, cfg):
+    """Size-independent properties of the prefill: processing the prompt in position chunks
+    (later chunks attend to the cache with a position offset) gives the logits of one chunk, and
+    the tcgen05 attention / persistent GEMM give the logits of the mma.sync / per-tile kernels."""
+    C = cuda_bf16
+    batch, seq = 2, 600
+    dec = cg.Decoder(C, cfg, max_seq=seq + 2, max_batch=batch)
+    dec.load(synth.make_weights(cfg, 0))
+    prompt = C.from_numpy(synth.make_tokens(cfg, batch, seq, seed=5))
+    ref = C.to_numpy(dec.prefill(prompt, want_logits=True))
+    try:
+        C.set_option("prefill_chunk", 256)  # 128 positions per chunk and row
+        chunked = C.to_numpy(dec.prefill(prompt, want_logits=True))
+        C.set_option("prefill_chunk", 8192)
+        C.set_option("fa", 0)
+        C.set_option("persistent", 0)
+        legacy = C.to_numpy(dec.prefill(prompt, want_logits=True))
+    finally:
+        C.set_option("prefill_chunk", 8192)
+        C.set_option("fa", 1)
+        C.set_option("persistent", 1)
+    np.testing.assert_allclose(chunked, ref, rtol=0, atol=2e-2)
+    np.testing.assert_allclose(legacy, ref, rtol=0, atol=2e-2)
+    dec.close()
