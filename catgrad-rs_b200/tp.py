@@ -8,6 +8,8 @@ until the output projections, the vocabulary until the arg-max):
 * gate/up:           rows of the rank's FFN slice        (column parallel)
 * down:              columns of the rank's FFN slice     (row parallel  -> all-reduce)
 * LM head:           rows of the rank's vocabulary slice (all-gather of logits, then arg-max)
+* experts:           whole experts per rank; every rank routes all tokens, runs the experts it
+                     owns, and the partial sums meet in the same all-reduce as a row-parallel GEMM
 
 `shard_plan` is the index arithmetic (the native decoder applies the same ranges when it
 keeps its shard of the full tensors it is handed); `init_comm` carries the NCCL unique id
@@ -22,13 +24,23 @@ def shard_plan(cfg, rank: int, world: int) -> dict:
     """Row/column ranges (start, stop) of every sharded parameter for `rank` of `world`."""
     nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.get_head_dim()
     F, V = cfg.intermediate_size, cfg.vocab_size
-    if nh % world or nkv % world or F % world or V % world:
-        raise ValueError("heads, kv heads, ffn and vocab must divide by the tensor-parallel degree")
+    E = getattr(cfg, "num_local_experts", 0)
+    # fewer kv heads than ranks: every kv head is replicated on world / nkv consecutive ranks
+    kv_ok = nkv % world == 0 or (nkv < world and world % nkv == 0)
+    if nh % world or not kv_ok or F % world or V % world or (E > 1 and E % world):
+        raise ValueError("heads, kv heads, ffn, vocab and experts must divide by the tensor-parallel degree")
     q = (rank * (nh // world) * d, (rank + 1) * (nh // world) * d)
-    kv = (rank * (nkv // world) * d, (rank + 1) * (nkv // world) * d)
+    if nkv >= world:
+        kv = (rank * (nkv // world) * d, (rank + 1) * (nkv // world) * d)
+    else:
+        head = rank * nkv // world  # the kv head this rank's query heads belong to
+        kv = (head * d, (head + 1) * d)
     f = (rank * (F // world), (rank + 1) * (F // world))
     v = (rank * (V // world), (rank + 1) * (V // world))
-    return {"q_rows": q, "kv_rows": kv, "o_cols": q, "ffn_rows": f, "down_cols": f, "vocab_rows": v}
+    plan = {"q_rows": q, "kv_rows": kv, "o_cols": q, "ffn_rows": f, "down_cols": f, "vocab_rows": v}
+    if E > 1:
+        plan["experts"] = (rank * (E // world), (rank + 1) * (E // world))  # whole experts per rank
+    return plan
 
 
 def init_comm(backend, rank: int, world: int) -> None:

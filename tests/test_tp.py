@@ -56,6 +56,32 @@ WORKER = textwrap.dedent("""
     flat = gathered.transpose(1, 0, 2).reshape(3, -1)          # global index = part * Vp + i
     pick = flat.shape[1] - 1 - np.argmax(flat[:, ::-1], axis=1)
     assert pick.tolist() == [100, 127, 100]
+    # expert parallelism by ownership: each rank sums the experts it owns, the all-reduce adds up
+    mcfg = cg.synth.ModelConfig("ep-test", 32, 64, 1, 4, 2, 64, head_dim=8, arch="qwen3", num_local_experts=8,
+                                num_experts_per_tok=3, moe_intermediate_size=16, norm_topk_prob=True)
+    e0, e1 = cg.tp.shard_plan(mcfg, rank, world)["experts"]
+    rng = np.random.Generator(np.random.PCG64(9))
+    xs = rng.standard_normal((5, 32)).astype(np.float32)
+    wr = rng.standard_normal((8, 32)).astype(np.float32)
+    wg = rng.standard_normal((8, 16, 32)).astype(np.float32) * 0.1
+    wu = rng.standard_normal((8, 16, 32)).astype(np.float32) * 0.1
+    wd = rng.standard_normal((8, 32, 16)).astype(np.float32) * 0.1
+    lg = xs @ wr.T
+    pr = np.exp(lg - lg.max(1, keepdims=True)); pr /= pr.sum(1, keepdims=True)
+    ids = np.argsort(-pr, axis=1, kind="stable")[:, :3]                # ties -> lower expert id
+    wt = np.take_along_axis(pr, ids, 1); wt /= wt.sum(1, keepdims=True)
+    def expert(e, v):
+        g = wg[e] @ v; u = wu[e] @ v
+        return wd[e] @ (g / (1 + np.exp(-g)) * u)
+    full = np.zeros_like(xs); part = np.zeros_like(xs)
+    for t in range(5):
+        for s_ in range(3):
+            y = wt[t, s_] * expert(ids[t, s_], xs[t])
+            full[t] += y
+            if e0 <= ids[t, s_] < e1:
+                part[t] += y
+    t = torch.from_numpy(part.copy()); dist.all_reduce(t)
+    assert np.allclose(t.numpy(), full, rtol=1e-5, atol=1e-6)
     dist.destroy_process_group()
     print("tp worker ok", rank)
 """)
@@ -82,6 +108,11 @@ def test_shard_plan_ranges():
     assert seen_v[-1][1] == cfg.vocab_size
     with pytest.raises(ValueError):
         cg.tp.shard_plan(cfg, 0, 3)
+    # fewer kv heads than ranks: replicated kv heads (4 kv heads on 8 ranks -> ranks 2h, 2h+1 share head h)
+    q = cg.synth.QWEN3_30B_A3B
+    heads = [cg.tp.shard_plan(q, r, 8)["kv_rows"][0] // q.head_dim for r in range(8)]
+    assert heads == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert [cg.tp.shard_plan(q, r, 8)["experts"] for r in (0, 7)] == [(0, 16), (112, 128)]
 
 
 GPU_WORKER = textwrap.dedent("""
