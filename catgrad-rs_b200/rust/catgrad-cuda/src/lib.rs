@@ -12,6 +12,7 @@
 // relies on.  A non-zero status panics with the library's message, like the existing backends
 // (ndarray.rs:212,255,293,333; candle.rs:413-415).
 mod ffi;
+pub mod decoder;
 
 use catgrad::category::core::{Dtype, Shape};
 use catgrad::interpreter::backend::{Backend, BackendError, BackendTensorOps};
@@ -40,6 +41,9 @@ unsafe impl Sync for CudaTensor {}
 impl Clone for CudaTensor {
     fn clone(&self) -> Self { unsafe { ffi::cg_tensor_retain(self.0); } CudaTensor(self.0) }
 }
+impl CudaTensor {
+    pub(crate) fn raw(&self) -> *const ffi::cg_tensor { self.0 }
+}
 impl Drop for CudaTensor { fn drop(&mut self) { unsafe { ffi::cg_tensor_release(self.0); } } }
 impl std::fmt::Debug for CudaTensor {
     fn fmt(&self, f: &mut std::fmt::Formatter<'_>) -> std::fmt::Result { write!(f, "CudaTensor{:?}", self.shape()) }
@@ -62,7 +66,8 @@ impl CudaBackend {
         assert_eq!(st, 0, "cg_ctx_create failed: no CUDA device? (there is no CPU fallback)");
         CudaBackend { ctx: Arc::new(Ctx(ctx)) }
     }
-    fn check(&self, st: i32) {
+    pub(crate) fn raw_ctx(&self) -> *mut ffi::cg_ctx { self.ctx.0 }
+    pub(crate) fn check(&self, st: i32) {
         if st != 0 {
             let msg = unsafe { CStr::from_ptr(ffi::cg_last_error(self.ctx.0)) }.to_string_lossy().into_owned();
             panic!("{msg}");
