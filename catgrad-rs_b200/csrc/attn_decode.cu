@@ -39,8 +39,11 @@ __device__ __forceinline__ float ld_dsmem(uint32_t local_addr, uint32_t rank) {
   return v;
 }
 
+// KT = keys per warp tile: 32, or 16 for head size 256 so that a CTA's tiles fit a third of an
+// SM's shared memory.
 template <int D>
 __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
+  constexpr int KT = D > 128 ? 16 : 32;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int LD = D + 8;     // padded rows: conflict-free ldmatrix
@@ -48,9 +51,9 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
   constexpr int NT = D / 8;     // output n-tiles
   extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* qt = (__nv_bfloat16*)smem;              // [16][LD] query heads (rows >= rep are zero)
-  __nv_bfloat16* kt = qt + 16 * LD;                      // [4 warps][32][LD] key tiles
-  __nv_bfloat16* vt = kt + 4 * 32 * LD;                  // [4 warps][32][LD] value tiles
-  float* fl = (float*)(vt + 4 * 32 * LD);
+  __nv_bfloat16* kt = qt + 16 * LD;                      // [4 warps][KT][LD] key tiles
+  __nv_bfloat16* vt = kt + 4 * KT * LD;                  // [4 warps][KT][LD] value tiles
+  float* fl = (float*)(vt + 4 * KT * LD);
   float* knew = fl;                                      // [D] the new key (bf16-rounded)
   float* vnew = knew + D;                                // [D]
   float* red_m = vnew + D;                               // [4][MAX_REP]
@@ -72,19 +75,19 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
   if (a.window > 0) lo = max((int64_t)0, pos - a.window + 1);
   const int64_t span = pos - lo;
   int64_t per = (span + a.splits - 1) / a.splits;
-  per = (per + 31) / 32 * 32;
+  per = (per + KT - 1) / KT * KT;
   const int64_t t0 = lo + split * per, t1 = min(pos, t0 + per);
 
-  __nv_bfloat16* kw = kt + (size_t)warp * 32 * LD;
-  __nv_bfloat16* vw = vt + (size_t)warp * 32 * LD;
+  __nv_bfloat16* kw = kt + (size_t)warp * KT * LD;
+  __nv_bfloat16* vw = vt + (size_t)warp * KT * LD;
   const uint32_t kw_u = (uint32_t)__cvta_generic_to_shared(kw);
   const uint32_t vw_u = (uint32_t)__cvta_generic_to_shared(vw);
   const uint32_t qt_u = (uint32_t)__cvta_generic_to_shared(qt);
 
   // request the first chunk of this warp now: it does not depend on q
   auto request = [&](int64_t c0) {
-    // 32 rows x CH chunks, 8 (or more) lanes per row: fully coalesced 16-byte copies
-    for (int i = lane; i < 32 * CH; i += 32) {
+    // KT rows x CH chunks, 8 (or more) lanes per row: fully coalesced 16-byte copies
+    for (int i = lane; i < KT * CH; i += 32) {
       const int r = i / CH, ch = i - r * CH;
       const int64_t key = c0 + r;
       const bool ok = key < t1;
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
       cp_async16(vw_u + (uint32_t)(r * LD + ch * 8) * 2u, vbase + kc * (int64_t)D + ch * 8, ok ? 16 : 0);
     }
   };
-  int64_t c0 = t0 + warp * 32;
+  int64_t c0 = t0 + warp * KT;
   if (c0 < t1) request(c0);
 
   // ---- 1. q, k, v of the new token ----
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
         kw[e] = __float2bfloat16_rn(knew[e]);
         vw[e] = __float2bfloat16_rn(vnew[e]);
       }
-      for (int i = lane; i < 31 * CH; i += 32) {
+      for (int i = lane; i < (KT - 1) * CH; i += 32) {
         const int r = 1 + i / CH, ch = i % CH;
         *(uint4*)(vw + r * LD + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // p = 0 times NaN garbage must not happen
         *(uint4*)(kw + r * LD + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
@@ -193,9 +196,9 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
     }
     const int64_t cbase = do_new ? 0 : c0;
 
-    float s[4][4];
+    float s[KT / 8][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       uint32_t a0, a1, a2, a3;
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
         ldsm_x4(qt_u + (uint32_t)(r * LD + col) * 2u, a0, a1, a2, a3);
       }
 #pragma unroll
-      for (int j = 0; j < 4; j += 2) {
+      for (int j = 0; j < KT / 8; j += 2) {
         uint32_t b0, b1, b2, b3;
         const int key = j * 8 + (lane & 7) + 8 * (lane >> 4);
         const int col = kk * 16 + 8 * ((lane >> 3) & 1);
@@ -217,7 +220,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
     // scale, soft-cap, mask; this head's maximum over the chunk
     float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         float v = s[j][e] * scale;
@@ -234,7 +237,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
     const float corr = __expf(m - mnew);
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const float p = __expf(s[j][e] - mnew);
@@ -253,7 +256,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
     }
     // O += P V; rows 8..15 of P are zero
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
+    for (int kk = 0; kk < KT / 16; ++kk) {
       const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
       const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
 #pragma unroll
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
     }
     __syncwarp();
     if (do_new) break;
-    c0 += 4 * 32;
+    c0 += 4 * KT;
     if (c0 < t1) request(c0);
   }
 
@@ -345,7 +348,8 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
 template <int D>
 int launch(cg_ctx* c, const AttnDecArgs& a) {
   constexpr int LD = D + 8;
-  const size_t smem = (size_t)(16 * LD + 8 * 32 * LD) * 2 + (size_t)(2 * D + 8 * MAX_REP + 16) * 4;
+  constexpr int KT = D > 128 ? 16 : 32;
+  const size_t smem = (size_t)(16 * LD + 8 * KT * LD) * 2 + (size_t)(2 * D + 8 * MAX_REP + 16) * 4;
   static PerDeviceFlag configured_on;
   bool& configured = configured_on.at(c->core->device);
   if (!configured && smem > 48 * 1024) {
@@ -371,10 +375,10 @@ int launch(cg_ctx* c, const AttnDecArgs& a) {
 int attn_dec_splits(int64_t Tmax, int64_t pairs, int d) {
   int s = 1;
   while (s < 8 && (int64_t)s * 128 < Tmax) s *= 2;
-  // head size 256: a CTA needs 143 KB of shared memory, one CTA per SM, and a cluster of 8 such
-  // CTAs needs 8 free SMs in one GPC -- fewer clusters fit than there are SMs (measured: 128
-  // CTAs took two waves).  Clusters of 4 place freely.
-  if (d > 128 && s > 4) s = 4;
+  // (head size 256 once had 32-key tiles: 143 KB per CTA, one CTA per SM, and clusters of 8 such
+  // CTAs did not all fit at once -- 128 CTAs took two waves; with 16-key tiles three CTAs share
+  // an SM)
+  (void)d;
   // (16 slices -- a cluster size this GPU supports beyond the portable 8 -- were measured for
   // few (row, kv head) pairs with long contexts and were slower: 2.92 -> 3.15 ms per step on
   // the 256-wide heads of the Gemma shape.)
