@@ -166,6 +166,9 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "handover" : 1 (default) = in decode steps of pre-norm models the residual GEMMs also leave
  *             the gain-scaled bf16 activations and per-row sums of squares, and the next GEMM
  *             applies 1 / rms in its epilogue (no separate norm kernel); 0 = norm kernels
+ *   "fa"    : 1 (default) = prefill attention on tcgen05 / TMEM for head sizes 64 and 128 without
+ *             soft-cap or window (2 = its 64-key-tile variant); 0 = the mma.sync kernel everywhere
+ *   "prefill_chunk" : tokens per prefill chunk (default 8192; bounds the decoder's workspace)
  *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
  *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
  *             decode step, and identically on every rank.
