@@ -332,7 +332,7 @@ bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 
 // supports), about two CTAs per SM in total, at least two k blocks per CTA
 static int dec_splits(int64_t tiles, int kb_total) {
   int splits = 1;
-  while (splits < 16 && tiles * (splits * 2) <= 2 * 148 + 32 && kb_total / (splits * 2) >= 2) splits *= 2;
+  while (splits < 16 && tiles * (splits * 2) <= 3 * 148 && kb_total / (splits * 2) >= 2) splits *= 2;
   const int kb_per = (kb_total + splits - 1) / splits;
   if ((kb_total + kb_per - 1) / kb_per != splits) splits = 1;  // an empty slice would break the cluster shape
   return splits;
