@@ -329,7 +329,7 @@ int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const De
 bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 8 == 0; }
 
 // split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this GPU
-// supports), about two CTAs per SM in total, at least two k blocks per CTA
+// supports), at most about three CTAs per SM in total, at least two k blocks per CTA
 static int dec_splits(int64_t tiles, int kb_total) {
   int splits = 1;
   while (splits < 16 && tiles * (splits * 2) <= 3 * 148 && kb_total / (splits * 2) >= 2) splits *= 2;
