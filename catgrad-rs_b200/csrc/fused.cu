@@ -255,6 +255,40 @@ __global__ void k_rope_store(RopeStoreArgs a) {
   }
 }
 
+// The same without per-head norms (Llama, Gemma-2), vectorised: one thread per four elements of
+// a head -- for q and k the rotation pairs (j, j + 1) and (j + d/2, j + d/2 + 1), for v four
+// consecutive values -- with 64-bit loads and 32-bit bf16x2 stores, contiguous across a warp.
+__global__ void k_rope_store_vec(RopeStoreArgs a) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int heads = a.nh + 2 * a.nkv;
+  const int d = a.d, half = d / 2, per_head = d / 4;
+  const int64_t total = a.M * heads * per_head;
+  const int64_t pos00 = a.pos_dev ? *a.pos_dev : a.pos0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t mh = i / per_head;
+    const int t = (int)(i - mh * per_head);
+    const int64_t m = mh / heads;
+    const int h = (int)(mh - m * heads);
+    const int64_t b = m / a.S, pos = pos00 + (m - b * a.S);
+    const float* src = a.qkv + mh * d;
+    if (h >= a.nh + a.nkv) {
+      const float4 v = ((const float4*)src)[t];
+      __nv_bfloat16* dst = a.v_cache + ((b * a.nkv + (h - a.nh - a.nkv)) * a.Tmax + pos) * d + 4 * t;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      *(uint2*)dst = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+      continue;
+    }
+    const int j = 2 * t;
+    const float2 x1 = *(const float2*)(src + j), x2 = *(const float2*)(src + j + half);
+    const float2 c = *(const float2*)(a.cos_t + pos * half + j), sn = *(const float2*)(a.sin_t + pos * half + j);
+    __nv_bfloat16* dst = h < a.nh ? a.q_out + m * (int64_t)a.nh * d + (int64_t)h * d
+                                  : a.k_cache + ((b * a.nkv + (h - a.nh)) * a.Tmax + pos) * d;
+    *(__nv_bfloat162*)(dst + j) = __floats2bfloat162_rn(c.x * x1.x - sn.x * x2.x, c.y * x1.y - sn.y * x2.y);
+    *(__nv_bfloat162*)(dst + j + half) = __floats2bfloat162_rn(c.x * x2.x + sn.x * x1.x, c.y * x2.y + sn.y * x1.y);
+  }
+}
+
 // argmax over the vocabulary with the reference's ordering (total order on the bit patterns,
 // last index wins ties), in two launches: every block folds a slice of one row into
 // (key << 32 | index) and merges it into best[row] with a 64-bit atomic max, which is
@@ -477,6 +511,12 @@ int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* co
 int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
   const int64_t warps = a.M * (a.nh + 2 * a.nkv);
   if (warps == 0) return CG_OK;
+  if (!a.q_gamma && !a.k_gamma && a.d % 8 == 0) {
+    const int64_t items = warps * (a.d / 4);
+    CG_CUDA(c, launch_kernel(c, k_rope_store_vec, dim3(grid_for(items, 256, 148 * 32)), dim3(256), 0, 1, a));
+    CG_LAUNCHED(c);
+    return CG_OK;
+  }
   const int block = 256;
   const int64_t blocks = (warps * 32 + block - 1) / block;
   CG_CUDA(c, launch_kernel(c, k_rope_store, dim3((unsigned)blocks), dim3(block), 0, 1, a));
