@@ -86,6 +86,21 @@ __global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float
   }
   ss = block_sum(ss, sh);
   const float rms = sqrtf(ss / (float)H + eps);
+  if (MODE == 1 && vec && (((uintptr_t)gamma & 15) == 0)) {
+    // bf16 output: 128-bit loads (the row is hot in L1 / L2 after the first pass), 64-bit stores
+    const float4* r4 = (const float4*)row;
+    const float4* g4 = (const float4*)gamma;
+    uint2* o2 = (uint2*)((__nv_bfloat16*)out + m * H);
+    for (int64_t i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      const float4 v = r4[i];
+      float4 g = g4[i];
+      if (plus_one) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x / rms * g.x, v.y / rms * g.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z / rms * g.z, v.w / rms * g.w);
+      o2[i] = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
     const float g = plus_one ? 1.f + gamma[i] : gamma[i];
     const float v = row[i] / rms * g;
