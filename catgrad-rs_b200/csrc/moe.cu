@@ -281,8 +281,11 @@ __global__ void k_moe_plan(const uint32_t* ids, int P, int e_lo, int El, int tn,
 
 // xg[pos[p], :] = xn[p / k, :] (bf16 rows of H elements, H % 8 == 0)
 __global__ void k_moe_gather(const __nv_bfloat16* xn, const int32_t* pos, int64_t P, int k, int H, __nv_bfloat16* xg) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The launch trigger comes AFTER this kernel's own dependency wait: a dependent that starts
+  // early can then rely on the planning kernel (this kernel's predecessor) being complete, i.e.
+  // read the tile list and stream its expert weights while the rows are still being gathered.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int per = H / 8;
   const int64_t total = P * per;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -362,8 +365,10 @@ k_moe_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   constexpr uint32_t NCOLS = ACC_COLS < 32 ? 32 : ACC_COLS;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // the tile list is written by the preceding kernels
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The tile list was complete before this kernel could start (k_moe_gather raises its launch
+  // trigger only after its wait on the planning kernel), so it is read -- and the weight tiles
+  // it names are requested -- before this kernel's own dependency wait; only the gathered
+  // activations and the stores wait for the predecessor.
   const int t = blockIdx.y;
   if (t >= *p.n_tiles) return;  // uniform over the CTA, before anything is allocated
   const int expert = p.tile_expert[t], row0 = p.tile_row0[t], rows = p.tile_rows[t];
@@ -384,7 +389,7 @@ k_moe_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bars + 8 * s, 1);             // full[s]: one expect_tx covering all boxes of the stage
+      mbar_init(bars + 8 * s, 2);             // full[s]: weight arrival + activation arrival
       mbar_init(bars + 8 * (STAGES + s), 1);  // empty[s]: one tcgen05.commit
     }
     mbar_init(bar_accum, 1);
@@ -406,18 +411,28 @@ k_moe_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   bool acc_ok = false;
   if (warp == 0) {
     if (lane == 0) {
+      const int pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {  // weights of the first stages: no dependency
+        const uint32_t full = bars + 8 * i;
+        const uint32_t a = base + i * STAGE_BYTES;
+        mbar_expect_tx(full, W_BYTES);
+        tma_load_2d(a, &map_w, i * BK, wrow, full);
+        if (DUAL) tma_load_2d(a + A_BYTES, &map_u, i * BK, wrow, full);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES;
         const uint32_t full = bars + 8 * s;
         const uint32_t a = base + s * STAGE_BYTES;
         const int k = i * BK;
-        if (i >= STAGES) {
+        if (i >= pre) {
           const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
           if (!mbar_wait(bars + 8 * (STAGES + s), ph ^ 1u, cta_abort, p.err)) break;
+          mbar_expect_tx(full, W_BYTES);
+          tma_load_2d(a, &map_w, k, wrow, full);
+          if (DUAL) tma_load_2d(a + A_BYTES, &map_u, k, wrow, full);
         }
-        mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(a, &map_w, k, wrow, full);
-        if (DUAL) tma_load_2d(a + A_BYTES, &map_u, k, wrow, full);
+        mbar_expect_tx(full, B_BYTES);
         tma_load_2d(a + W_BYTES, &map_x, k, row0, full);
       }
     }
@@ -443,6 +458,8 @@ k_moe_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
       if (ok) umma_commit(bar_accum);
     }
   } else {
+    // the stores belong to the stream order
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     acc_ok = mbar_wait(bar_accum, 0, cta_abort, p.err);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
