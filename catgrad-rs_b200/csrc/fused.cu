@@ -270,9 +270,11 @@ __global__ void k_rope_store(RopeStoreArgs a) {
   }
 }
 
-// The same without per-head norms (Llama, Gemma-2), vectorised: one thread per four elements of
-// a head -- for q and k the rotation pairs (j, j + 1) and (j + d/2, j + d/2 + 1), for v four
-// consecutive values -- with 64-bit loads and 32-bit bf16x2 stores, contiguous across a warp.
+// The same vectorised, for head sizes up to 128: one thread per four elements of a head -- for q
+// and k the rotation pairs (j, j + 1) and (j + d/2, j + d/2 + 1), for v four consecutive values
+// -- with 64-bit loads and 32-bit bf16x2 stores, contiguous across a warp.  The d/4 threads of a
+// head are consecutive lanes of one warp, so the optional per-head RMSNorm is a shuffle
+// reduction among them.
 __global__ void k_rope_store_vec(RopeStoreArgs a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -295,7 +297,18 @@ __global__ void k_rope_store_vec(RopeStoreArgs a) {
       continue;
     }
     const int j = 2 * t;
-    const float2 x1 = *(const float2*)(src + j), x2 = *(const float2*)(src + j + half);
+    float2 x1 = *(const float2*)(src + j), x2 = *(const float2*)(src + j + half);
+    const float* gamma = h < a.nh ? a.q_gamma : a.k_gamma;
+    if (gamma) {
+      float ss = x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y;
+      const unsigned live = __activemask();  // whole heads are in or out of range together
+      for (int o = per_head / 2; o; o >>= 1) ss += __shfl_xor_sync(live, ss, o);
+      const float inv = 1.f / sqrtf(ss / (float)d + a.norm_eps);
+      float2 g1 = *(const float2*)(gamma + j), g2 = *(const float2*)(gamma + j + half);
+      if (a.norm_plus_one) { g1.x += 1.f; g1.y += 1.f; g2.x += 1.f; g2.y += 1.f; }
+      x1.x = x1.x * inv * g1.x; x1.y = x1.y * inv * g1.y;
+      x2.x = x2.x * inv * g2.x; x2.y = x2.y * inv * g2.y;
+    }
     const float2 c = *(const float2*)(a.cos_t + pos * half + j), sn = *(const float2*)(a.sin_t + pos * half + j);
     __nv_bfloat16* dst = h < a.nh ? a.q_out + m * (int64_t)a.nh * d + (int64_t)h * d
                                   : a.k_cache + ((b * a.nkv + (h - a.nh)) * a.Tmax + pos) * d;
@@ -526,7 +539,7 @@ int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* co
 int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
   const int64_t warps = a.M * (a.nh + 2 * a.nkv);
   if (warps == 0) return CG_OK;
-  if (!a.q_gamma && !a.k_gamma && a.d % 8 == 0) {
+  if (a.d % 8 == 0 && ((!a.q_gamma && !a.k_gamma) || (a.q_gamma && a.k_gamma && a.d <= 128 && (128 % a.d) == 0))) {
     const int64_t items = warps * (a.d / 4);
     CG_CUDA(c, launch_kernel(c, k_rope_store_vec, dim3(grid_for(items, 256, 148 * 32)), dim3(256), 0, 1, a));
     CG_LAUNCHED(c);
