@@ -221,7 +221,7 @@ __global__ void k_moe_topk(const float* logits, int64_t M, int E, int k, int nor
   }
 }
 
-// One block of 1024 threads (El <= 1024).  Counts the pairs routed to experts
+// One block of at least El threads (El <= 1024).  Counts the pairs routed to experts
 // [e_lo, e_lo + El), lays the groups out back to back, lists the GEMM tiles (tn rows each,
 // never crossing a group) and gives every pair its row (or -1 when another rank owns its
 // expert).  Thread e owns expert e: two block-wide prefix sums give its first row and its
@@ -592,7 +592,9 @@ int moe_ffn(cg_ctx* c, const MoeArgs& a) {
                              a.H, a.E, a.k, a.norm_topk, a.xn, a.w.ids, a.w.wts));
     CG_LAUNCHED(c);
   }
-  CG_CUDA(c, launch_kernel(c, k_moe_plan, dim3(1), dim3(1024), (size_t)a.El * 8, 1, (const uint32_t*)a.w.ids, (int)P, a.e_lo,
+  // one thread per local expert is the minimum; more threads only help the histogram of a long prompt
+  const unsigned plan_threads = P > 4096 ? 1024u : (unsigned)std::max(128, (a.El + 31) / 32 * 32);
+  CG_CUDA(c, launch_kernel(c, k_moe_plan, dim3(1), dim3(plan_threads), (size_t)a.El * 8, 1, (const uint32_t*)a.w.ids, (int)P, a.e_lo,
                            a.El, tn, a.w.pos, a.w.tile_expert, a.w.tile_row0, a.w.tile_rows, a.w.n_tiles));
   CG_LAUNCHED(c);
   CG_CUDA(c, launch_kernel(c, k_moe_gather, dim3(grid_for(P * (a.H / 8), 256)), dim3(256), 0, 1, (const __nv_bfloat16*)a.xn,
