@@ -52,3 +52,24 @@ def test_decoder_config_mirror_matches_header():
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
     fields = re.findall(r"\b(?:int32_t|float)\s+([a-z_0-9]+)\s*;", body)
     assert fields == [f[0] for f in cg.DecoderConfig._fields_]
+
+
+def test_rust_shim_mirrors_match_header():
+    """The Rust binding is source only (no toolchain here), so its ABI mirrors are checked as
+    text: the decoder configuration has the header's fields in the header's order and types, and
+    every extern function the shim declares exists in the header."""
+    text = open(os.path.join(ROOT, "include", "catgrad_cuda.h")).read()
+    body = text[text.index("typedef struct cg_decoder_config {"):text.index("} cg_decoder_config;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    want = [(n, "f32" if t == "float" else "i32") for t, n in re.findall(r"\b(int32_t|float)\s+([a-z_0-9]+)\s*;", body)]
+    rust_dir = os.path.join(ROOT, "catgrad-rs_b200", "rust", "catgrad-cuda", "src")
+    rs = open(os.path.join(rust_dir, "decoder.rs")).read()
+    struct = rs[rs.index("pub struct DecoderConfig {"):]
+    struct = struct[:struct.index("}")]
+    got = re.findall(r"pub\s+([a-z_0-9]+)\s*:\s*(i32|f32)\s*,", struct)
+    assert got == want
+    product = set(declared(os.path.join(ROOT, "include", "catgrad_cuda.h"), "cg_"))
+    for name in ("ffi.rs", "decoder.rs"):
+        src = open(os.path.join(rust_dir, name)).read()
+        for fn in re.findall(r"\bfn\s+(cg_[a-z0-9_]+)\s*\(", src):
+            assert fn in product, (name, fn)
