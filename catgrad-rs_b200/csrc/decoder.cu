@@ -10,6 +10,11 @@
 // decode step is the same kernel sequence: it is captured once into a CUDA graph and
 // replayed.
 //
+// A decode step of a dense pre-norm layer is five kernels -- qkv GEMM, fused attention, o GEMM,
+// paired gate/up GEMM, down GEMM -- with the RMSNorms folded into the GEMMs around them (see
+// DecGemm in kernels.h); prefill runs the persistent tensor-core GEMMs and the tcgen05
+// attention.  Mixture-of-experts layers (moe.cu) and post-norm models keep their norm kernels.
+//
 // Data layout in HBM (per rank; heads, FFN columns and vocabulary are sharded over tp_world):
 //   w_qkv   [ (nh + 2 nkv) d, H ] bf16   rows = q heads, then k heads, then v heads
 //   w_o     [ H, nh d ]           bf16

@@ -16,6 +16,13 @@
 //     thread-block cluster (deterministic), then the epilogue (residual add / bf16 / act)
 //     is applied once.
 //
+//   * two optional hand-overs ride on the epilogue.  Norm hand-over: a residual GEMM also
+//     leaves bf16(out * gain) and per-CTA sums of out^2, and the GEMM behind the norm applies
+//     1 / rms per row to its accumulators (RMSNorm(x) W^T = (x gain) W^T / rms(x)), so decode
+//     steps of pre-norm models run no norm kernels.  Push: under tensor parallelism the partial
+//     product goes straight into every rank's mapped exchange area and the last CTA raises
+//     this rank's flag there (peer.cuh), instead of a collective call.
+//
 // All waits are bounded; on expiry the context's error word is raised and the kernel still
 // passes its cluster barriers, frees its TMEM and returns.
 #include <algorithm>
