@@ -3,13 +3,16 @@
 One "step" is one whole job on synthetic data: prefill of B x PROMPT token ids followed by
 DECODE greedy steps, for all B rows.  The metric is tokens per second over prompt and
 generated tokens.  `value` is timed on the device with the token ids already resident in
-HBM; `e2e` is the same job through the host-buffer entry point (ids copied host->device,
-every step's tokens read back device->host).
+HBM; `e2e` is the same job through the host-buffer entry point (ids copied host->device, all
+steps enqueued back to back, the token history [B, 1 + DECODE] read back device->host in one
+strided copy at the end).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 N > 1 is launched by torchrun, one rank per GPU; the model is tensor-parallel over the N
-ranks (NCCL all-reduce after the two row-split projections of every layer).
+ranks.  Decode steps exchange the partial products of the two row-split projections of every
+layer through mapped peer memory (plain stores and flags, no collective call); prefill uses an
+NCCL all-reduce with a bf16 payload.
 
 `--impl reference` times the CPU restatement of the reference's ndarray backend running the
 reference's own op stream (one full forward per generated token, no KV cache) on the host
@@ -150,6 +153,40 @@ def run_reference_sample(cg, cfg, prompt_len: int, threads: int = 0):
     return forward, cores
 
 
+def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local):
+    """Compare the token history [B, 1 + T] the timed job produced with an independent run that
+    is teacher-forced with those tokens (so one flipped near-tie does not cascade): at one GPU
+    the same decoder stepping one kernel per operation, eagerly, one step at a time; under tensor
+    parallelism a complete one-GPU decoder that rank 0 builds next to its shard.  Reports the
+    fraction of equal tokens and where they differ."""
+    if rank != 0 or job_tokens is None:
+        return None
+    B = prompt.shape[0]
+    if world == 1:
+        other, vs = dec, "the same decoder run eagerly, one kernel per operation, one step per call"
+        C.set_option("resident", 0)
+    else:
+        other = cg.Decoder(C, cfg, max_seq=prompt.shape[1] + T + 1, max_batch=B, tp_rank=0, tp_world=1)
+        other.load(cg.synth.make_weights(cfg, 0))
+        vs = "a one-GPU (tp_world = 1) decoder built by rank 0 on its own GPU"
+    try:
+        other.reset()
+        other.prefill(C.from_numpy(prompt))
+        for i in range(T):
+            other.step_with(C.from_numpy(np.ascontiguousarray(job_tokens[:, i])))
+        mine = other.tokens()
+    finally:
+        if world == 1:
+            C.set_option("resident", 1)
+        else:
+            other.close()
+    eq = mine == job_tokens
+    bad = np.argwhere(~eq)
+    return {"tokens_equal_frac": float(eq.mean()), "vs": vs, "compared": int(eq.size), "disagreements": int((~eq).sum()),
+            "first_disagreements_row_step": [[int(r), int(c)] for r, c in bad[:8]],
+            "how": "teacher-forced with the job's tokens; every step's greedy pick compared"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,6 +321,11 @@ def main():
     ms_e2e = timed(job_host, args.steps)
     clocks = sampler.stop()
 
+    # what was timed is checked: the job's greedy tokens against an independent run
+    token_check = check_tokens(cg, C, dec, cfg, prompt, out_tokens, T, rank, world, local)
+    if dist is not None:
+        dist.barrier()
+
     # phase split and the kernel-level roofline, measured live
     ms_prefill = timed(lambda: dec.prefill(prompt_dev), args.steps) / args.steps
     dec.prefill(prompt_dev)
@@ -332,6 +374,9 @@ def main():
                    "decode_step_bytes": {"dense_weights": weight_bytes, "kv_cache": kv_bytes,
                                          "experts_expected": expert_bytes}},
     }
+    if token_check is not None:
+        line["tokens_equal_frac"] = token_check["tokens_equal_frac"]
+        line["token_check"] = token_check
     if rank == 0 and world == 1 and not args.no_cpu_baseline and headline:
         forward, cores = run_reference_sample(cg, dataclasses.replace(cfg, dtype="bf16"), S)
         t_fwd = forward()
@@ -345,6 +390,9 @@ def main():
     dec.close()
     if dist is not None:
         dist.destroy_process_group()
+    if token_check is not None and token_check["tokens_equal_frac"] < 0.9:
+        raise SystemExit(f"token check failed: only {token_check['tokens_equal_frac']:.3f} of the job's tokens equal the "
+                         "independent run's")
 
 
 if __name__ == "__main__":

@@ -335,6 +335,7 @@ class CudaBackend(TraitBackend):
             ("cg_linear", [vp, vp, vp, out], i32),
             ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
             ("cg_randn", [vp, _c_i64p, i32, C.c_uint64, f32, f32, out], i32),
+            ("cg_probe_wait_timeout", [vp], i32),
         ]:
             fn = getattr(L, name)
             fn.argtypes = args
@@ -361,6 +362,10 @@ class CudaBackend(TraitBackend):
 
     def set_option(self, name: str, value: int):
         self._check(self._lib.cg_set_option(self._ctx, name.encode(), int(value)))
+
+    def probe_wait_timeout(self):
+        """Enqueue the failure-path probe: a bounded wait on a flag nothing raises."""
+        self._check(self._lib.cg_probe_wait_timeout(self._ctx))
 
     def storage_of(self, x) -> int:
         s = C.c_int32()

@@ -64,6 +64,7 @@ struct cg_decoder {
   std::vector<Layer> layers;
   cg_tensor *embed = nullptr, *head = nullptr, *ln_f = nullptr;
   cg_tensor *cos_t = nullptr, *sin_t = nullptr;
+  cg_tensor *cos_l = nullptr, *sin_l = nullptr;  // tables of the second rope base (gemma3.rs:154-159), or null
   // state
   cg_tensor* state = nullptr;     // int64[2] on device: {position, tokens generated}
   cg_tensor* cur = nullptr;       // u32 [B]: the tokens the next step consumes
@@ -88,6 +89,7 @@ struct cg_decoder {
   bool logits_gathered = true;   // `logits` holds every rank's slice
   cudaGraphExec_t graph = nullptr;
   int64_t graph_B = -1;
+  int64_t graph_gen = -1;        // option generation the graph was captured under
   int64_t step_launches = 0;     // kernels in one decode step
   int64_t splitk_floats = 0;
 
@@ -278,6 +280,15 @@ int all_reduce_f32(cg_decoder* D, float* p, int64_t n) {
   return CG_OK;
 }
 
+int all_reduce_bf16(cg_decoder* D, __nv_bfloat16* p, int64_t n) {
+  cg_ctx* c = D->c;
+  if (D->cfg.tp_world <= 1) return CG_OK;
+  if (!c->comm) return fail(c, CG_ERR_COMM, "decoder: tensor parallelism needs cg_comm_init first");
+  ncclResult_t r = nccl().AllReduce(p, p, (size_t)n, ncclBfloat16, ncclSum, (ncclComm_t)c->comm, c->core->stream);
+  if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllReduce: ") + nccl().GetErrorString(r));
+  return CG_OK;
+}
+
 // x += W-projection of `xin` (row-split under tensor parallelism), optionally through a
 // post-norm: x += rmsnorm(proj).
 int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor* w, const cg_tensor* post_norm, bool push,
@@ -290,6 +301,18 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
   if (push) return gemm(D, xin, M, w, nullptr, nullptr, 3);
   if (!tp && !post_norm) return gemm(D, xin, M, w, x, x, 2);
   float* t = (float*)D->tmp->data();
+  if (tp && !post_norm && !small_m(M, D->H) && D->H % 2 == 0) {
+    // prefill: the partial products travel as bf16 (half the bytes of the f32 residual stream;
+    // the all-reduce is bandwidth-bound at these sizes), and one pass adds the reduced rows to
+    // the replicated f32 residual and writes the norm the next block starts with.  Every rank
+    // receives the same reduced rows, so the residual stream stays bit-identical across ranks.
+    __nv_bfloat16* tb = (__nv_bfloat16*)D->tmp->data();
+    CG_TRY(gemm(D, xin, M, w, tb, nullptr, 1));
+    CG_TRY(all_reduce_bf16(D, tb, M * D->H));
+    if (next_norm) D->xn_ready = true;
+    return k_launch_add_bf16_norm(c, tb, next_norm ? (const float*)next_norm->data() : nullptr, D->cfg.rms_eps,
+                                  D->cfg.norm_plus_one, M, D->H, x, (__nv_bfloat16*)D->xn->data());
+  }
   if (tp && !post_norm) {
     // in place: rank 0 leaves x + partial in x, every other rank just its partial (its copy of
     // the old x is identical to rank 0's and no longer needed); the sum over ranks is the new
@@ -343,12 +366,16 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     D->xn_ready = false;
     CG_TRY(gemm(D, D->xn, M, L.w_qkv, D->qkvb->data(), nullptr, 0, false, nullptr, D->xn_raw));
     D->xn_raw = false;
+    // layers off the pattern rotate with the local base (gemma3.rs:154-159)
+    const bool local_rope = D->cos_l && cfg.rope_local_every > 0 && (li + 1) % cfg.rope_local_every != 0;
+    const float* cos_t = (const float*)(local_rope ? D->cos_l : D->cos_t)->data();
+    const float* sin_t = (const float*)(local_rope ? D->sin_l : D->sin_t)->data();
     const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
     if (S == 1) {
       AttnDecArgs f;
       f.qkv = (const float*)D->qkvb->data();
-      f.cos_t = (const float*)D->cos_t->data();
-      f.sin_t = (const float*)D->sin_t->data();
+      f.cos_t = cos_t;
+      f.sin_t = sin_t;
       f.q_gamma = L.q_norm ? (const float*)L.q_norm->data() : nullptr;
       f.k_gamma = L.k_norm ? (const float*)L.k_norm->data() : nullptr;
       f.norm_eps = cfg.rms_eps;
@@ -366,8 +393,8 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     } else {
     RopeStoreArgs r;
     r.qkv = (const float*)D->qkvb->data();
-    r.cos_t = (const float*)D->cos_t->data();
-    r.sin_t = (const float*)D->sin_t->data();
+    r.cos_t = cos_t;
+    r.sin_t = sin_t;
     r.q_gamma = L.q_norm ? (const float*)L.q_norm->data() : nullptr;
     r.k_gamma = L.k_norm ? (const float*)L.k_norm->data() : nullptr;
     r.norm_eps = cfg.rms_eps;
@@ -570,7 +597,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
     drop(L.router); drop(L.router3); drop(L.we_gate); drop(L.we_up); drop(L.we_down);
   }
   if (D->head != D->embed) drop(D->head);
-  drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->state); drop(D->cur); drop(D->history);
+  drop(D->embed); drop(D->ln_f); drop(D->cos_t); drop(D->sin_t); drop(D->cos_l); drop(D->sin_l); drop(D->state); drop(D->cur); drop(D->history);
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->hact);
   drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best); drop(D->ss);
   drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
@@ -725,6 +752,11 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->cos_t));
   CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->sin_t));
   CG_TRY(k_launch_rope_tables(c, cfg.rope_theta, cfg.max_seq, d, (float*)D->cos_t->data(), (float*)D->sin_t->data()));
+  if (cfg.rope_local_theta > 0.f && cfg.rope_local_every > 0) {
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->cos_l));
+    CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->sin_l));
+    CG_TRY(k_launch_rope_tables(c, cfg.rope_local_theta, cfg.max_seq, d, (float*)D->cos_l->data(), (float*)D->sin_l->data()));
+  }
 
   int64_t n = 4;
   CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &D->state));  // 16 bytes: two int64
@@ -804,7 +836,7 @@ int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) 
   if (D->pos + steps > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: KV cache capacity exceeded");
   if (steps == 0) return logits_copy(D, logits_out);
   cudaStream_t s = c->core->stream;
-  if (!D->graph || D->graph_B != D->B) {
+  if (!D->graph || D->graph_B != D->B || D->graph_gen != c->opt_generation) {
     if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }
     // Run one step eagerly first: it configures kernel attributes and surfaces errors
     // outside of capture.  Then capture the identical sequence.
@@ -825,6 +857,7 @@ int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) 
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return cuda_fail(c, e, "cudaGraphInstantiate");
     D->graph_B = D->B;
+    D->graph_gen = c->opt_generation;
   }
   for (int i = 0; i < steps; ++i) CG_CUDA(c, cudaGraphLaunch(D->graph, s));
   c->launches += (int64_t)steps * D->step_launches;  // each replay runs the captured kernels

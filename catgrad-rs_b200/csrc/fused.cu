@@ -139,6 +139,39 @@ __global__ void k_rmsnorm_add_norm(const float* y, const float* g1, const float*
   }
 }
 
+// Tensor-parallel prefill: the row-parallel projections meet in a bf16 all-reduce; this adds the
+// reduced rows to the f32 residual stream, x += t, and in the same pass writes the norm the next
+// block starts with, out = bf16(rmsnorm(x; g)) (g null: the add only).  One block per row.
+__global__ void k_add_bf16_norm(const __nv_bfloat16* t, const float* g, float eps, int plus_one, int64_t H, float* x,
+                                __nv_bfloat16* out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float sh[32];
+  const int64_t m = blockIdx.x;
+  const __nv_bfloat162* tr = (const __nv_bfloat162*)(t + m * H);
+  float2* xr = (float2*)(x + m * H);
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) {
+    const float2 a = __bfloat1622float2(tr[i]);
+    float2 v = xr[i];
+    v.x += a.x;
+    v.y += a.y;
+    xr[i] = v;
+    ss += v.x * v.x + v.y * v.y;
+  }
+  if (!g) return;
+  ss = block_sum(ss, sh);
+  const float rms = sqrtf(ss / (float)H + eps);
+  __nv_bfloat162* o = (__nv_bfloat162*)(out + m * H);
+  const float2* g2 = (const float2*)g;
+  for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) {
+    const float2 v = xr[i];  // this thread's own store above
+    float2 gg = g2[i];
+    if (plus_one) { gg.x += 1.f; gg.y += 1.f; }
+    o[i] = __floats2bfloat162_rn(v.x / rms * gg.x, v.y / rms * gg.y);
+  }
+}
+
 __global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* out) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -519,6 +552,16 @@ int k_launch_rmsnorm_add_norm(cg_ctx* c, const float* y, const float* g1, const 
   return CG_OK;
 }
 
+int k_launch_add_bf16_norm(cg_ctx* c, const __nv_bfloat16* t, const float* g, float eps, int plus_one, int64_t M, int64_t H,
+                           float* x, __nv_bfloat16* out) {
+  if (M == 0) return CG_OK;
+  if (H % 2) return fail(c, CG_ERR_UNSUPPORTED, "add + norm: the row length must be even");
+  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  CG_CUDA(c, launch_kernel(c, k_add_bf16_norm, dim3((unsigned)M), dim3(block), 0, 1, t, g, eps, plus_one, H, x, out));
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
 int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out) {
   if (M == 0 || F == 0) return CG_OK;
   dim3 grid((unsigned)std::min<int64_t>((F / 4 + 255) / 256 + 1, 64), (unsigned)M);
@@ -596,6 +639,9 @@ int k_launch_argmax_tp(cg_ctx* c, const PeerPush& px, float* logits, int64_t B, 
   CG_LAUNCHED(c);
   return CG_OK;
 }
+
+// waits on a word of the error block that stays zero
+__global__ void k_probe_wait(int32_t* err) { peer_wait_flag((const uint32_t*)(err + 8), 1u, err); }
 
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out) {
   if (n == 0) return CG_OK;
@@ -755,3 +801,10 @@ int32_t cg_randn(cg_ctx* c, const int64_t* dims, int32_t rank, uint64_t seed, fl
 }
 
 }  // extern "C"
+
+extern "C" int32_t cg_probe_wait_timeout(cg_ctx* c) {
+  if (!c) return CG_ERR_INVALID;
+  cg::k_probe_wait<<<1, 1, 0, c->core->stream>>>(c->core->dev_err);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}

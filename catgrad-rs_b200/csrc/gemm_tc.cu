@@ -375,6 +375,12 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
 
   Hold ws;
   if (splits > 1 && !cluster && !workspace) {
+    // A block taken from the caching allocator here is recycled when this call returns; a graph
+    // captured now would keep writing to it on every replay, whoever owns it by then.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(c->core->stream, &cap);
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(c, CG_ERR_INVALID, "gemm_tc: split-K workspace must be passed in while the stream is being captured");
     int64_t n = (int64_t)splits * M * N;
     CG_TRY(new_tensor(c, CG_F32, ST_F32, &n, 1, &ws.t));
     workspace = (float*)ws.t->data();

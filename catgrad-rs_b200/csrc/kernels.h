@@ -25,6 +25,11 @@ int k_launch_rmsnorm_add(cg_ctx* c, const float* y, const float* gamma, float ep
 int k_launch_rmsnorm_add_norm(cg_ctx* c, const float* y, const float* g1, const float* g2, float eps, int plus_one, int64_t M,
                               int64_t H, float* x, __nv_bfloat16* out);
 
+// x += t (bf16 rows into the f32 residual stream) and, when g is non-null, out = bf16(rmsnorm(x; g))
+// in the same pass: the tail of a tensor-parallel row-parallel projection after its bf16 all-reduce.
+int k_launch_add_bf16_norm(cg_ctx* c, const __nv_bfloat16* t, const float* g, float eps, int plus_one, int64_t M, int64_t H,
+                           float* x, __nv_bfloat16* out);
+
 // act(gu[m, 0:F]) * gu[m, F:2F] -> bf16 [M, F]; act 0 = silu, 1 = tanh-gelu.
 int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, __nv_bfloat16* out);
 

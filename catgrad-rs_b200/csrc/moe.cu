@@ -44,6 +44,26 @@ __device__ __forceinline__ float block_sum_f(float v, float* sh) {
   return v;  // every thread of every warp holds the total
 }
 
+// Sum of the k values held one per lane (lane r holds value r, k <= 32) in the order of the
+// reference's reduction: ndarray folds a contiguous lane with eight interleaved partial sums,
+// combines them as ((p0+p4)+(p1+p5))+((p2+p6)+(p3+p7)) and adds the tail in order (the checker's
+// lane_sum).  Called by all 32 lanes; every lane gets the same bits.
+__device__ __forceinline__ float sum_in_reference_order(float mine, int k) {
+  float p[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int i = 0;
+  for (; i + 8 <= k; i += 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = p[j] + __shfl_sync(0xffffffffu, mine, i + j);
+  }
+  float acc = 0.f;
+  acc = acc + (p[0] + p[4]);
+  acc = acc + (p[1] + p[5]);
+  acc = acc + (p[2] + p[6]);
+  acc = acc + (p[3] + p[7]);
+  for (; i < k; ++i) acc = acc + __shfl_sync(0xffffffffu, mine, i);
+  return acc;
+}
+
 // One block per token.  Shared memory: xs[H] normalised row, pr[E] router probabilities.
 __global__ void k_moe_route(const float* x, const float* gamma, float eps, int plus_one, const float* wr, int H, int E, int k,
                             int norm_topk, __nv_bfloat16* xn, uint32_t* ids, float* wts) {
@@ -108,11 +128,11 @@ __global__ void k_moe_route(const float* x, const float* gamma, float eps, int p
     }
     const uint32_t e = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
     const float v = __uint_as_float((uint32_t)(best >> 32));
-    total += v;  // same order as the reference's sum over the k values
     if (lane == r) { chosen = v; chosen_id = e; }  // k <= 32: slot r lives in lane r
     if (lane == 0) pr[e] = -1.f;
     __syncwarp();
   }
+  total = sum_in_reference_order(chosen, k);  // bit-identical to the reference's sum over the k values
   if (lane < k) {
     ids[m * k + lane] = chosen_id;
     wts[m * k + lane] = norm_topk ? chosen / total : chosen;
@@ -210,11 +230,11 @@ __global__ void k_moe_topk(const float* logits, int64_t M, int E, int k, int nor
     }
     const uint32_t e = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
     const float v = __uint_as_float((uint32_t)(best >> 32));
-    total += v;
     if (lane == r) { chosen = v; chosen_id = e; }
     if (lane == 0) pr[e] = -1.f;
     __syncwarp();
   }
+  total = sum_in_reference_order(chosen, k);  // bit-identical to the reference's sum over the k values
   if (lane < k) {
     ids[m * k + lane] = chosen_id;
     wts[m * k + lane] = norm_topk ? chosen / total : chosen;

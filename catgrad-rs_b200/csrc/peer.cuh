@@ -8,18 +8,25 @@
 namespace cg {
 
 // Bounded wait until a flag written by another GPU reaches `want`; on expiry raises the
-// context's error word and gives up (the caller carries on with whatever data is there).
+// context's error word and gives up (the caller carries on with whatever data is there).  Once a
+// timeout has been reported in this context, every later wait gives up at its first slow-path
+// check: a rank that stopped pushing costs the others one limit in total, not one per hand-over.
+// The limit is the 64-bit word at byte offset 8 of the error block (nanoseconds, 0 = 1 s).
 __device__ __forceinline__ bool peer_wait_flag(const uint32_t* f, uint32_t want, int32_t* err) {
-  unsigned long long t0 = 0;
+  unsigned long long t0 = 0, limit = 0;
   for (uint32_t it = 0;; ++it) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
     if (v == want) return true;
     if ((it & 0xFF) == 0xFF) {
+      if (*(volatile int32_t*)err == DEV_TIMEOUT) return false;
       unsigned long long now;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) { *err = DEV_TIMEOUT; return false; }
+      if (t0 == 0) {
+        t0 = now;
+        limit = *(const volatile unsigned long long*)(err + 2);
+        if (limit == 0) limit = 1000000000ull;
+      } else if (now - t0 > limit) { *err = DEV_TIMEOUT; return false; }
     }
   }
 }

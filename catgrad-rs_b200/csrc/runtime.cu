@@ -272,7 +272,17 @@ int64_t cg_bytes_reserved(cg_ctx* c) { return c ? c->core->reserved : 0; }
 
 int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
   if (!c || !name) return CG_ERR_INVALID;
+  c->opt_generation++;  // decoders re-capture their step graph when a switch may have changed the kernel sequence
   if (!strcmp(name, "gemm")) { c->opt_gemm = (int)value; return CG_OK; }
+  if (!strcmp(name, "wait_limit_us")) {
+    // limit of every bounded device-side wait (mbarrier, peer flag, grid barrier)
+    if (value < 1 || value > 60ll * 1000 * 1000) return fail(c, CG_ERR_INVALID, "wait_limit_us out of range");
+    const unsigned long long ns = (unsigned long long)value * 1000ull;
+    CG_CUDA(c, cudaMemcpyAsync((char*)c->core->dev_err + 8, &ns, 8, cudaMemcpyHostToDevice, c->core->stream));
+    CG_CUDA(c, cudaStreamSynchronize(c->core->stream));  // `ns` is on the stack
+    return CG_OK;
+  }
+  if (!strcmp(name, "resident")) { c->opt_resident = value != 0; return CG_OK; }
   if (!strcmp(name, "pdl")) { c->opt_pdl = value != 0; return CG_OK; }
   if (!strcmp(name, "peer")) { c->opt_peer = value != 0; return CG_OK; }
   if (!strcmp(name, "fa")) { c->opt_fa = (int)value; return CG_OK; }

@@ -28,11 +28,19 @@ __device__ __forceinline__ uint64_t globaltimer() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait on an mbarrier phase.  Returns false (and raises *err) after ~1 s or once
-// another wait of this CTA has already given up.
+// The context's device error block: word 0 is the error code (DevErr), the 64-bit word at byte
+// offset 8 is the limit of every bounded wait in nanoseconds (set by the host; 0 reads as 1 s).
+__device__ __forceinline__ uint64_t wait_limit_ns(const int32_t* err) {
+  const uint64_t v = *(const volatile uint64_t*)(err + 2);
+  return v ? v : 1000000000ull;
+}
+// Bounded wait on an mbarrier phase.  Returns false once the limit has passed (raising *err),
+// once another wait of this CTA has already given up, or once any kernel of the context has
+// reported a timeout: after the first expiry every later wait gives up at its first slow-path
+// check, so a lost producer costs one limit in total instead of one per wait.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int32_t* err) {
   uint32_t done = 0;
-  uint64_t t0 = 0;
+  uint64_t t0 = 0, limit = 0;
   for (uint32_t it = 0;; ++it) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -44,9 +52,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (done) return true;
     if ((it & 0x3FF) == 0x3FF) {
       if (*cta_abort) return false;
+      if (*(volatile int32_t*)err == DEV_TIMEOUT) break;
       uint64_t now = globaltimer();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) break;
+      if (t0 == 0) { t0 = now; limit = wait_limit_ns(err); }
+      else if (now - t0 > limit) break;
     }
   }
   *cta_abort = 1;

@@ -23,6 +23,7 @@ class DecoderConfig(C.Structure):
         ("qk_norm", C.c_int32), ("act", C.c_int32), ("norm_plus_one", C.c_int32), ("post_norms", C.c_int32),
         ("embed_scale", C.c_float), ("attn_softcap", C.c_float), ("final_softcap", C.c_float),
         ("sliding_window", C.c_int32), ("window_every", C.c_int32),
+        ("rope_local_theta", C.c_float), ("rope_local_every", C.c_int32),
         ("n_experts", C.c_int32), ("top_k", C.c_int32), ("moe_ffn", C.c_int32), ("norm_topk", C.c_int32),
         ("tp_rank", C.c_int32), ("tp_world", C.c_int32),
     ]
@@ -83,6 +84,9 @@ class Decoder:
             c.final_softcap = cfg.final_logit_softcap
             c.sliding_window = cfg.sliding_window
             c.window_every = 2
+            if getattr(cfg, "sliding_window_pattern", 0) > 0 and getattr(cfg, "rope_local_base_freq", 0.0) > 0:
+                c.rope_local_theta = cfg.rope_local_base_freq
+                c.rope_local_every = cfg.sliding_window_pattern
         if getattr(cfg, "num_local_experts", 0) > 1:
             # mixture-of-experts FFN on the layers whose checkpoint carries a router (qwen3.rs:297-298)
             c.n_experts = cfg.num_local_experts

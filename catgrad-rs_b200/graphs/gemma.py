@@ -3,8 +3,9 @@ reference tree lacks (attention logit soft-cap, final logit soft-cap, sliding-wi
 composed from reference ops: cap * tanh(x / cap) with the stdlib's tanh
 (catgrad/src/stdlib/nn/mod.rs:138-144) and a second `lt` on the arange grids of
 `causal_mask` (catgrad-llm/src/helpers.rs:239-257).  With qk_norm=False, one rope base and the
-soft-caps/window set, this is the Gemma-2-shaped benchmark configuration; with qk_norm=True and
-no caps it is the reference's Gemma3 graph (single rope base)."""
+soft-caps/window set, this is the Gemma-2-shaped benchmark configuration; with qk_norm=True, no
+caps and sliding_window_pattern / rope_local_base_freq set it is the reference's Gemma3 graph,
+whose local layers rotate with their own rope base (gemma3.rs:154-159)."""
 from __future__ import annotations
 
 import numpy as np
@@ -64,8 +65,13 @@ def attention(B, cfg, params, layer_id, pos, p, x):
         k = rmsnorm(B, cfg.rms_norm_eps, params, p + ".k_norm", k)
         q = B.reshape(q, (b, nh, s, hd))
         k = B.reshape(k, (b, nkv, s, hd))
-    q = H.rope(B, cfg.rope_theta, pos, s, hd, q)   # tables rebuilt per call (gemma3.rs:160-161)
-    k = H.rope(B, cfg.rope_theta, pos, s, hd, k)
+    # every sliding_window_pattern-th layer is global, the others local, with different rope
+    # frequencies (gemma3.rs:154-159); tables rebuilt per call (gemma3.rs:160-161)
+    theta = cfg.rope_theta
+    if cfg.sliding_window_pattern > 0 and (layer_id + 1) % cfg.sliding_window_pattern != 0:
+        theta = cfg.rope_local_base_freq
+    q = H.rope(B, theta, pos, s, hd, q)
+    k = H.rope(B, theta, pos, s, hd, k)
     k = H.repeat_kv(B, rep, k)
     v = H.repeat_kv(B, rep, v)
     attn = B.matmul(q, B.transpose(k, 2, 3))

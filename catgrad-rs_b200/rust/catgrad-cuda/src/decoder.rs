@@ -35,6 +35,8 @@ pub struct DecoderConfig {
     pub final_softcap: f32,
     pub sliding_window: i32,
     pub window_every: i32,
+    pub rope_local_theta: f32,
+    pub rope_local_every: i32,
     pub n_experts: i32,
     pub top_k: i32,
     pub moe_ffn: i32,

@@ -41,6 +41,10 @@ class ModelConfig:
     attn_logit_softcap: float = 0.0
     final_logit_softcap: float = 0.0
     sliding_window: int = 0           # 0 = none; even layers use it when set
+    # gemma3.rs:154-159: layers with (i + 1) % sliding_window_pattern != 0 rotate q/k with
+    # rope_local_base_freq, the others with rope_theta (0 = one base everywhere)
+    sliding_window_pattern: int = 0
+    rope_local_base_freq: float = 0.0
     extras: dict = field(default_factory=dict)
 
     def __post_init__(self):

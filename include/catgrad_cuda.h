@@ -172,8 +172,21 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
  *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
  *             decode step, and identically on every rank.
+ *   "resident" : 1 (default) = decode steps of dense pre-norm models on one GPU run as ONE
+ *             resident kernel for all requested steps (weights streamed through a shared-memory
+ *             ring that never drains between the GEMMs of a step); 0 = one kernel per operation
+ *   "wait_limit_us" : limit of every bounded device-side wait (default 1 000 000).  When a wait
+ *             runs out the kernel gives up, later waits of the context give up at once, and the
+ *             next cg_sync returns CG_ERR_TIMEOUT and clears the condition.
+ * A decoder re-captures its decode-step graph after any option change.
  */
 int32_t cg_set_option(cg_ctx*, const char* name, int64_t value);
+
+/* Failure-path probe: enqueues one small kernel that waits (bounded by "wait_limit_us") on a
+ * flag of the context that nothing ever raises.  The wait runs out, the kernel returns, and the
+ * next cg_sync reports CG_ERR_TIMEOUT; the context stays usable.  Nothing faults or traps.
+ * No counterpart in the reference (its backends have no device-side waits). */
+int32_t cg_probe_wait_timeout(cg_ctx*);
 
 /* Storage precision of a tensor: 0 = f32, 1 = u32, 2 = bf16 (F32 tag stored as bf16). */
 int32_t cg_storage_of(const cg_tensor* t, int32_t* storage);
@@ -255,6 +268,9 @@ typedef struct cg_decoder_config {
   float final_softcap;
   int32_t sliding_window;   /* 0 = none */
   int32_t window_every;     /* layers with (i % window_every) != window_every-1 use the window */
+  float rope_local_theta;   /* 0 = one rope base; else the base of "local" layers (gemma3.rs:154-159) */
+  int32_t rope_local_every; /* layers with (i + 1) % rope_local_every != 0 rotate with rope_local_theta,
+                               the others with rope_theta (the reference's sliding_window_pattern) */
   /* mixture of experts (qwen3.rs:64-133): a layer whose checkpoint carries a router
    * ("...mlp.gate.weight" [n_experts, hidden]) and stacked experts
    * ("...mlp.experts.{gate,up,down}_proj.weight") runs the expert block instead of the dense FFN */
@@ -293,9 +309,10 @@ int32_t cg_decoder_step_with(cg_decoder*, const cg_tensor* tokens, cg_tensor** l
 /* Tokens generated so far as a device U32 tensor [B, n_generated] (prefill's token first). */
 int32_t cg_decoder_tokens(cg_decoder*, cg_tensor** out);
 /* The call the reference's example driver makes, end to end, with HOST buffers: copies
- * `prompt` [B*S] to the device, prefills, then runs n_decode steps reading each step's
- * tokens back to the host like the reference's per-step to_vec (examples/llama/main.rs:160).
- * `out` receives [B, 1 + n_decode] tokens. */
+ * `prompt` [B*S] to the device, prefills, then enqueues n_decode steps back to back (the device
+ * feeds each step's arg-max to the next, where the reference's host loop reads every token back
+ * with to_vec, examples/llama/main.rs:160) and reads the token history back in one strided
+ * device-to-host copy at the end.  `out` receives [B, 1 + n_decode] tokens. */
 int32_t cg_decoder_generate(cg_decoder*, const uint32_t* prompt, int32_t batch, int32_t seq,
                             int32_t n_decode, uint32_t* out);
 

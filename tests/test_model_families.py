@@ -21,8 +21,10 @@ QWEN_MOE = synth.ModelConfig("qwen3-moe-small", 128, 256, 2, 4, 2, 512, head_dim
 GEMMA2 = synth.ModelConfig("gemma2-small", 256, 512, 2, 4, 2, 1024, head_dim=64, arch="gemma", rope_theta=10000.0,
                            tie_word_embeddings=True, attn_logit_softcap=50.0, final_logit_softcap=30.0,
                            sliding_window=8)
-GEMMA3 = synth.ModelConfig("gemma3-small", 256, 512, 2, 4, 2, 1024, head_dim=64, arch="gemma", rope_theta=1e6,
-                           tie_word_embeddings=True, qk_norm=True)
+# three layers with pattern 2: local, global, local -- the local layers rotate with their own base
+GEMMA3 = synth.ModelConfig("gemma3-small", 256, 512, 3, 4, 2, 1024, head_dim=64, arch="gemma", rope_theta=1e6,
+                           tie_word_embeddings=True, qk_norm=True, sliding_window_pattern=2,
+                           rope_local_base_freq=10000.0)
 
 
 def fwd_of(cfg):

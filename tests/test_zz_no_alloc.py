@@ -17,6 +17,15 @@ from conftest import cg
 pytestmark = pytest.mark.gpu
 
 
+def total_order_argmax(x: np.ndarray) -> np.ndarray:
+    """Row-wise arg-max under f32::total_cmp, last index on ties, computed on the host with numpy
+    only (no library code): -NaN < -inf < ... < -0 < +0 < ... < +inf < +NaN."""
+    bits = x.view(np.uint32).astype(np.uint64)
+    key = np.where(bits & 0x80000000, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    n = x.shape[1]
+    return (n - 1 - np.argmax(key[:, ::-1], axis=1)).astype(np.uint32)   # first maximum of the reversed row
+
+
 def test_noalloc_argmax_matches_argmax_twice(cuda):
     import torch
 
@@ -25,11 +34,21 @@ def test_noalloc_argmax_matches_argmax_twice(cuda):
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_char_p, C.c_int64]
     fn.restype = C.c_int32
     rng = np.random.Generator(np.random.PCG64(11))
+    neg_nan = np.uint32(0xFFC00000).view(np.float32)
+    # long rows take the chunked reduction (64 chunks per row); one row holds nothing but -NaN and -inf
+    # except a late -inf run, one has +NaN in the middle, one is all -NaN (the smallest key there is)
+    long_rows = rng.standard_normal((4, 70000), dtype=np.float32)
+    long_rows[1, :] = neg_nan
+    long_rows[1, 123:60000] = -np.inf
+    long_rows[2, 40000] = np.nan
+    long_rows[3, :] = neg_nan
     cases = [rng.integers(0, 4, size=(37, 5000)).astype(np.float32),        # heavy ties: last index wins
              np.concatenate([rng.standard_normal((5, 130), dtype=np.float32),
-                             np.float32([[-0.0, 0.0] * 65, [np.nan] + [1.0] * 129])])]  # fewer rows the second time
+                             np.float32([[-0.0, 0.0] * 65, [np.nan] + [1.0] * 129])]),  # fewer rows the second time
+             long_rows]
     for x in cases:
         want = cuda.to_numpy(cuda.argmax(cuda.from_numpy(x))).ravel()     # existing entry point
+        np.testing.assert_array_equal(want, total_order_argmax(x))        # ... which agrees with the host expectation
         dx = torch.from_numpy(x).cuda()
         dout = torch.full((x.shape[0],), 0xFFFFFFF, dtype=torch.int32, device="cuda")
         err = C.create_string_buffer(256)
@@ -38,7 +57,8 @@ def test_noalloc_argmax_matches_argmax_twice(cuda):
         assert st == 0, err.value
         torch.cuda.synchronize()
         got = dout.cpu().numpy().astype(np.uint32)
-        np.testing.assert_array_equal(got, want)   # index work: bit-exact
+        np.testing.assert_array_equal(got, want)                          # index work: bit-exact
+        np.testing.assert_array_equal(got, total_order_argmax(x))         # and against numpy alone
 
 
 def test_noalloc_rejects_more_rows_than_its_scratch(cuda):
