@@ -164,7 +164,6 @@ def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local):
     B = prompt.shape[0]
     if world == 1:
         other, vs = dec, "the same decoder run eagerly, one kernel per operation, one step per call"
-        C.set_option("resident", 0)
     else:
         other = cg.Decoder(C, cfg, max_seq=prompt.shape[1] + T + 1, max_batch=B, tp_rank=0, tp_world=1)
         other.load(cg.synth.make_weights(cfg, 0))
@@ -176,9 +175,7 @@ def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local):
             other.step_with(C.from_numpy(np.ascontiguousarray(job_tokens[:, i])))
         mine = other.tokens()
     finally:
-        if world == 1:
-            C.set_option("resident", 1)
-        else:
+        if world > 1:
             other.close()
     eq = mine == job_tokens
     bad = np.argwhere(~eq)

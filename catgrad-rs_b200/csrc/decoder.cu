@@ -91,6 +91,10 @@ struct cg_decoder {
   int64_t graph_B = -1;
   int64_t graph_gen = -1;        // option generation the graph was captured under
   int64_t step_launches = 0;     // kernels in one decode step
+  // all steps of a decode call as one resident kernel (decode_resident.cu), when the model allows
+  ResidentPlan* rplan = nullptr;
+  int64_t rplan_B = -1, rplan_gen = -1;
+  bool resident_off = false;     // this model or device cannot take the resident kernel
   int64_t splitk_floats = 0;
 
   int64_t* pos_dev() { return (int64_t*)state->data(); }
@@ -140,6 +144,7 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   if (M <= D->cap) return CG_OK;
   cg_ctx* c = D->c;
   if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }  // it holds the old buffers
+  if (D->rplan) { decode_resident_free(D->rplan); D->rplan = nullptr; D->rplan_B = -1; }
   drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->hact); drop(D->tmp);
   const int64_t H = D->H;
   int64_t s2[2];
@@ -534,6 +539,68 @@ int logits_copy(cg_decoder* D, cg_tensor** out) {
   return CG_OK;
 }
 
+// The resident decode kernel serves dense pre-norm models on one GPU (Llama, dense Qwen3).
+bool resident_model(cg_decoder* D, ResidentModel* m) {
+  const cg_decoder_config& cfg = D->cfg;
+  if (cfg.tp_world != 1 || cfg.post_norms) return false;
+  for (const Layer& L : D->layers)
+    if (L.moe) return false;
+  m->layers.resize(D->layers.size());
+  for (size_t li = 0; li < D->layers.size(); ++li) {
+    const Layer& L = D->layers[li];
+    ResidentLayerDesc& d = m->layers[li];
+    d.w_qkv = (const __nv_bfloat16*)L.w_qkv->data(); d.w_o = (const __nv_bfloat16*)L.w_o->data();
+    d.w_gu = (const __nv_bfloat16*)L.w_gu->data(); d.w_down = (const __nv_bfloat16*)L.w_down->data();
+    d.gain_in = (const float*)L.ln_in->data(); d.gain_ffn = (const float*)L.ln_pre_ffn->data();
+    d.q_gamma = L.q_norm ? (const float*)L.q_norm->data() : nullptr;
+    d.k_gamma = L.k_norm ? (const float*)L.k_norm->data() : nullptr;
+    const bool local_rope = D->cos_l && cfg.rope_local_every > 0 && ((int)li + 1) % cfg.rope_local_every != 0;
+    d.cos_t = (const float*)(local_rope ? D->cos_l : D->cos_t)->data();
+    d.sin_t = (const float*)(local_rope ? D->sin_l : D->sin_t)->data();
+    d.k_cache = (__nv_bfloat16*)L.k_cache->data(); d.v_cache = (__nv_bfloat16*)L.v_cache->data();
+    const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || ((int)li % cfg.window_every) != cfg.window_every - 1);
+    d.window = windowed ? cfg.sliding_window : 0;
+  }
+  m->head = (const __nv_bfloat16*)D->head->data();
+  m->gain_final = (const float*)D->ln_f->data();
+  m->embed = D->embed->data();
+  m->embed_storage = D->embed->storage;
+  m->H = D->H; m->F = D->F; m->Vp = D->Vp; m->vocab = cfg.vocab; m->Tmax = cfg.max_seq;
+  m->nh = D->nh; m->nkv = D->nkv; m->d = D->d; m->act = cfg.act; m->plus_one = cfg.norm_plus_one;
+  m->eps = cfg.rms_eps; m->attn_softcap = cfg.attn_softcap; m->final_softcap = cfg.final_softcap;
+  m->embed_scale = cfg.embed_scale > 0.f ? cfg.embed_scale : 1.f;
+  m->x = (float*)D->x->data(); m->xn = (__nv_bfloat16*)D->xn->data();
+  m->ss = (float*)D->ss->data(); m->ss_parts_cap = SS_MAX_PARTS;
+  m->qkv = (float*)D->qkvb->data(); m->att = (__nv_bfloat16*)D->att->data(); m->hact = (__nv_bfloat16*)D->hact->data();
+  m->logits = (float*)D->logits->data();
+  m->cur = (uint32_t*)D->cur->data(); m->history = (uint32_t*)D->history->data(); m->hist_ld = cfg.max_seq;
+  m->count_dev = D->count_dev(); m->pos_dev = D->pos_dev();
+  m->best = (unsigned long long*)D->best->data();
+  return true;
+}
+
+// Runs `steps` decode steps on the resident kernel when the model and the context allow it.
+// *ran says whether it did.
+int try_resident(cg_decoder* D, int steps, bool* ran) {
+  *ran = false;
+  cg_ctx* c = D->c;
+  if (!c->opt_resident || D->resident_off) return CG_OK;
+  if (!D->rplan || D->rplan_B != D->B || D->rplan_gen != c->opt_generation) {
+    if (D->rplan) { decode_resident_free(D->rplan); D->rplan = nullptr; D->rplan_B = -1; }
+    ResidentModel m;
+    if (!resident_model(D, &m) || !decode_resident_supported(m, D->B)) { D->resident_off = true; return CG_OK; }
+    int st = decode_resident_prepare(c, m, D->B, &D->rplan);
+    if (st == CG_ERR_UNSUPPORTED) { D->resident_off = true; c->err.clear(); return CG_OK; }
+    CG_TRY(st);
+    D->rplan_B = D->B;
+    D->rplan_gen = c->opt_generation;
+  }
+  CG_TRY(decode_resident_run(c, D->rplan, steps));
+  D->logits_gathered = true;
+  *ran = true;
+  return CG_OK;
+}
+
 int set_state(cg_decoder* D, int64_t pos, int64_t generated) {
   int64_t v[2] = {pos, generated};
   CG_CUDA(D->c, cudaMemcpyAsync(D->state->data(), v, 16, cudaMemcpyHostToDevice, D->c->core->stream));
@@ -589,6 +656,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   if (!D) return CG_ERR_INVALID;
   cudaStreamSynchronize(D->c->core->stream);
   if (D->graph) cudaGraphExecDestroy(D->graph);
+  if (D->rplan) decode_resident_free(D->rplan);
   for (auto& kv : D->params) release(kv.second);
   for (auto& L : D->layers) {
     drop(L.w_qkv); drop(L.w_o); drop(L.w_gu); drop(L.w_down); drop(L.ln_in); drop(L.ln_post_attn);
@@ -835,6 +903,15 @@ int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) 
   if (!D->finalized || D->B == 0) return fail(c, CG_ERR_INVALID, "decoder: prefill first");
   if (D->pos + steps > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: KV cache capacity exceeded");
   if (steps == 0) return logits_copy(D, logits_out);
+  {
+    bool ran = false;
+    CG_TRY(try_resident(D, steps, &ran));
+    if (ran) {
+      D->pos += steps;
+      D->generated += steps;
+      return logits_copy(D, logits_out);
+    }
+  }
   cudaStream_t s = c->core->stream;
   if (!D->graph || D->graph_B != D->B || D->graph_gen != c->opt_generation) {
     if (D->graph) { cudaGraphExecDestroy(D->graph); D->graph = nullptr; }
@@ -875,7 +952,9 @@ int32_t cg_decoder_step_with(cg_decoder* D, const cg_tensor* tokens, cg_tensor**
   Hold tk;
   CG_TRY(as_contiguous(c, tokens, &tk.t));
   CG_CUDA(c, cudaMemcpyAsync(D->cur->data(), tk.t->data(), (size_t)D->B * 4, cudaMemcpyDeviceToDevice, c->core->stream));
-  CG_TRY(enqueue_step(D, D->B));
+  bool ran = false;
+  CG_TRY(try_resident(D, 1, &ran));
+  if (!ran) CG_TRY(enqueue_step(D, D->B));
   D->pos += 1;
   D->generated += 1;
   return logits_copy(D, logits_out);
@@ -917,6 +996,12 @@ int32_t cg_decoder_time_gemms(cg_decoder* D, int32_t batch, int32_t iters, float
   *ms_per_sweep = ms / (float)iters;
   if (launches_per_sweep) *launches_per_sweep = (int32_t)((c->launches - before) / iters);
   return cg_sync(c);
+}
+
+int32_t cg_decoder_resident_trace(cg_decoder* D, int32_t cta, uint64_t* out, int32_t n) {
+  if (!D) return CG_ERR_INVALID;
+  if (!D->rplan) return fail(D->c, CG_ERR_INVALID, "decoder: the resident kernel has not run yet");
+  return decode_resident_trace(D->c, D->rplan, cta, out, n);
 }
 
 int32_t cg_decoder_tokens(cg_decoder* D, cg_tensor** out) {

@@ -3,6 +3,8 @@
 // row-major unless a leading dimension is given.
 #pragma once
 
+#include <vector>
+
 #include "runtime.h"
 
 namespace cg {
@@ -206,6 +208,54 @@ struct MoeArgs {
 int moe_ffn(cg_ctx* c, const MoeArgs& a);
 int moe_pick_tn(int64_t pairs, int experts);
 int64_t moe_max_tiles(int64_t pairs, int experts_local, int tn);
+
+// All decode steps of a call as one resident kernel (decode_resident.cu): dense pre-norm
+// decoders on one GPU, at most 32 rows, head size 64 or 128.
+struct ResidentLayerDesc {
+  const __nv_bfloat16 *w_qkv, *w_o, *w_gu, *w_down;  // [(nh + 2 nkv) d, H], [H, nh d], [2 F, H], [H, F]
+  const float *gain_in, *gain_ffn;                    // input norm, pre-FFN norm
+  const float *q_gamma, *k_gamma;                     // per-head norms or null
+  const float *cos_t, *sin_t;                         // rotary tables [Tmax, d / 2]
+  __nv_bfloat16 *k_cache, *v_cache;                   // [B, nkv, Tmax, d]
+  int64_t window;                                     // 0 = none
+};
+struct ResidentModel {
+  std::vector<ResidentLayerDesc> layers;
+  const __nv_bfloat16* head;   // [Vp, H]
+  const float* gain_final;
+  const void* embed;           // [vocab, H] f32 or bf16
+  int embed_storage;
+  int64_t H, F, Vp, vocab, Tmax;
+  int nh, nkv, d, act, plus_one;
+  float eps, attn_softcap, final_softcap, embed_scale;
+  // workspace of the decoder (all device pointers)
+  float* x;                    // [M, H] residual stream
+  __nv_bfloat16* xn;           // [M, H]
+  float* ss;                   // [ss_parts_cap][32] partial sums of squares (used as two halves)
+  int64_t ss_parts_cap;
+  float* qkv;                  // [M, (nh + 2 nkv) d]
+  __nv_bfloat16* att;          // [M, nh d]
+  __nv_bfloat16* hact;         // [M, F]
+  float* logits;               // [M, Vp]
+  uint32_t* cur;               // [M] tokens of the next step
+  uint32_t* history;
+  int64_t hist_ld;
+  int64_t *count_dev, *pos_dev;
+  unsigned long long* best;    // [M] zeroed 64-bit merge slots
+};
+struct ResidentPlan;
+bool decode_resident_supported(const ResidentModel& m, int64_t M);
+// Builds the static schedule, tensor maps and device tables for M rows.
+int decode_resident_prepare(cg_ctx* c, const ResidentModel& m, int64_t M, ResidentPlan** out);
+// Enqueues n_steps decode steps: reads the tokens in `cur`, leaves the last pick there, appends
+// every pick to the history and advances the device counters by n_steps.
+int decode_resident_run(cg_ctx* c, ResidentPlan* plan, int n_steps);
+void decode_resident_free(ResidentPlan* plan);
+int64_t decode_resident_bytes_per_step(const ResidentPlan* plan);  // weight bytes one step streams
+int decode_resident_grid(const ResidentPlan* plan);                // resident CTAs
+// Diagnostics: out == null arms the timeline of CTA `cta` for the next run (cta < 0 disarms);
+// otherwise copies n globaltimer stamps (two per phase: may start, this CTA done) to the host.
+int decode_resident_trace(cg_ctx* c, ResidentPlan* plan, int cta, uint64_t* out, int n);
 
 // f32 -> bf16 rows (ld in elements for the source)
 int k_launch_to_bf16(cg_ctx* c, const float* x, int64_t n, __nv_bfloat16* out);

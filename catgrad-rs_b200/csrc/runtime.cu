@@ -283,6 +283,12 @@ int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
     return CG_OK;
   }
   if (!strcmp(name, "resident")) { c->opt_resident = value != 0; return CG_OK; }
+  if (!strcmp(name, "resident_stages")) { c->opt_res_stages = (int)value; return CG_OK; }
+  if (!strcmp(name, "resident_attn_group")) {
+    if (value != 0 && value != 1 && value != 2 && value != 4) return fail(c, CG_ERR_INVALID, "resident_attn_group must be 0, 1, 2 or 4");
+    c->opt_res_group = (int)value;
+    return CG_OK;
+  }
   if (!strcmp(name, "pdl")) { c->opt_pdl = value != 0; return CG_OK; }
   if (!strcmp(name, "peer")) { c->opt_peer = value != 0; return CG_OK; }
   if (!strcmp(name, "fa")) { c->opt_fa = (int)value; return CG_OK; }

@@ -87,7 +87,9 @@ struct cg_ctx {
   int opt_fa = 1;         // prefill attention on tcgen05 (attention_fa.cu) where it applies
   int opt_prefill_chunk = 8192;  // tokens per prefill chunk (bounds the decoder's workspace)
   int opt_peer = 1;       // small all-reduces over mapped peer memory instead of NCCL (when available)
-  int opt_resident = 1;   // decode steps of dense pre-norm models run as one resident kernel (decode_resident.cu)
+  int opt_resident = 0;   // 1: decode steps of dense pre-norm models run as one resident kernel (decode_resident.cu)
+  int opt_res_group = 0;  // resident decode: CTAs per (row, kv head) in the attention phase (0 = chosen by the library)
+  int opt_res_stages = 0;  // resident decode: cap on the ring depth (0 = as deep as shared memory allows)
   int64_t opt_generation = 0;  // bumped by every cg_set_option
   bool trace_on = false;  // record a device timeline of the decode GEMM launches
   int64_t trace_next = 0;

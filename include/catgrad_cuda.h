@@ -172,9 +172,14 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "peer"  : 1 (default) = decode steps under tensor parallelism reduce over mapped peer
  *             memory (see cg_comm_peer_exchange); 0 = NCCL collectives.  Set before the first
  *             decode step, and identically on every rank.
- *   "resident" : 1 (default) = decode steps of dense pre-norm models on one GPU run as ONE
- *             resident kernel for all requested steps (weights streamed through a shared-memory
- *             ring that never drains between the GEMMs of a step); 0 = one kernel per operation
+ *   "resident" : 1 = decode steps of dense pre-norm models on one GPU run as ONE resident kernel
+ *             for all requested steps (one CTA per SM, phases separated by bounded grid barriers,
+ *             weights streamed through a shared-memory ring that keeps filling across phase
+ *             boundaries); 0 (default) = one kernel per operation, captured into a CUDA graph.
+ *             Both give the same logits within bf16 rounding; the per-operation path is the
+ *             faster one at the measured shapes, so it stays the default.
+ *   "resident_attn_group" : CTAs that share one (row, kv head) in the resident kernel's attention
+ *             phase: 1, 2 or 4; 0 (default) = chosen from the batch and the cache length
  *   "wait_limit_us" : limit of every bounded device-side wait (default 1 000 000).  When a wait
  *             runs out the kernel gives up, later waits of the context give up at once, and the
  *             next cg_sync returns CG_ERR_TIMEOUT and clears the condition.
@@ -328,6 +333,13 @@ int32_t cg_decoder_time_gemms(cg_decoder*, int32_t batch, int32_t iters, float* 
  * ready, last CTA finished.  cg_trace_read copies `slots` x 4 values. */
 int32_t cg_trace_enable(cg_ctx*, int32_t on);
 int32_t cg_trace_read(cg_ctx*, uint64_t* out, int32_t slots);
+
+/* Diagnostics of the resident decode kernel ("resident" option): out == NULL arms a timeline of
+ * resident CTA `cta` for the next decode call (cta < 0 disarms); otherwise copies n globaltimer
+ * stamps in nanoseconds, two per phase of the schedule (embed, then per layer qkv GEMM,
+ * attention, o GEMM, gate/up GEMM, down GEMM, then the LM head; next step likewise): when the
+ * phase's grid barrier let the CTA through, and when the CTA finished its part of the phase. */
+int32_t cg_decoder_resident_trace(cg_decoder*, int32_t cta, uint64_t* out, int32_t n);
 
 /* Row-wise arg-max for callers that cannot allocate device memory (code that runs while
  * another stream of the process is being captured into a CUDA graph, plugins with a fixed memory

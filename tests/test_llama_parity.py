@@ -181,3 +181,49 @@ def test_chunked_prefill_equals_one_chunk_and_kernel_variants_agree(cuda_bf16, c
     np.testing.assert_allclose(chunked, ref, rtol=0, atol=2e-2)
     np.testing.assert_allclose(legacy, ref, rtol=0, atol=2e-2)
     dec.close()
+
+
+@pytest.mark.parametrize("cfg,batch,seq,steps", [(SMALL, 2, 24, 6), (SMALL, 8, 300, 12), (SMALL_D128, 3, 70, 4),
+                                                 (SMALL_D128, 20, 40, 6), (SMALL, 1, 1, 5)])
+def test_resident_decode_kernel_agrees_with_per_operation_path(cuda_bf16, cfg, batch, seq, steps):
+    """The "resident" option runs all decode steps of a call as one kernel (decode_resident.cu).
+    Its sums run in another order (K split four ways inside a cluster instead of up to sixteen),
+    so logits agree within bf16 rounding rather than bit for bit: teacher-forced with the default
+    path's tokens, every step's logits within 2e-2, and the greedy pick equal wherever the default
+    path's top-1 / top-2 margin exceeds twice that.  Batches above 16 take the 32-column tiles."""
+    C = cuda_bf16
+    dec = cg.Decoder(C, cfg, max_seq=seq + steps + 2, max_batch=batch)
+    dec.load(synth.make_weights(cfg, 0))
+    prompt = synth.make_tokens(cfg, batch, seq, seed=1)
+    dec.prefill(C.from_numpy(prompt))
+    dec.decode(steps)
+    toks = dec.tokens()
+
+    def forced(resident):
+        C.set_option("resident", resident)
+        dec.reset()
+        dec.prefill(C.from_numpy(prompt))
+        out = [C.to_numpy(dec.step_with(C.from_numpy(np.ascontiguousarray(toks[:, i])), want_logits=True))
+               for i in range(steps)]
+        return out, dec.tokens()
+
+    try:
+        l1, t1 = forced(1)
+        # one call for all steps: the kernel loops over the steps itself
+        dec.reset()
+        dec.prefill(C.from_numpy(prompt))
+        dec.decode(steps)
+        t_free = dec.tokens()
+        l0, t0 = forced(0)
+    finally:
+        C.set_option("resident", 0)
+    for a, b in zip(l0, l1):
+        assert np.abs(a - b).max() <= 2e-2
+        top2 = np.sort(a, axis=1)[:, -2:]
+        sure = top2[:, 1] - top2[:, 0] > 4e-2
+        assert (np.argmax(a, 1)[sure] == np.argmax(b, 1)[sure]).all()
+    assert (t0 == t1).mean() >= 0.9
+    # the multi-step call follows the same sequence as long as no near-tie flips a token
+    first_diff = np.argmax(np.concatenate([t_free != toks, np.ones((batch, 1), bool)], axis=1), axis=1)
+    assert (first_diff >= 1).all()   # the prefill's token is common to both
+    dec.close()
