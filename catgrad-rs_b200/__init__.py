@@ -7,6 +7,7 @@ The directory name is not a Python identifier; import it with
 * `graphs`   — the op streams of catgrad's stdlib and catgrad-llm model graphs
 * `decoder`  — the fused, KV-cached greedy runner
 * `synth`    — seeded synthetic checkpoints and prompts
+* `safetensors_io` — .safetensors checkpoint files: library-side reader, numpy writer
 * `tp`       — tensor-parallel sharding plan and communicator set-up
 * `build`    — the nvcc recipe for libcatgrad_cuda.so
 """
@@ -14,5 +15,5 @@ from .backend import (  # noqa: F401
     F32, U32, PREC_F32, PREC_BF16, BackendError, BackendPanic, TaggedTensor, TraitBackend,
     CudaBackend, load_library, library_path,
 )
-from . import graphs, synth, tp  # noqa: F401
+from . import graphs, safetensors_io, synth, tp  # noqa: F401
 from .decoder import Decoder, DecoderConfig  # noqa: F401

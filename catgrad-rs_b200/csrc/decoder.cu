@@ -28,10 +28,12 @@
 
 #include <cstring>
 #include <map>
+#include <memory>
 #include <string>
 
 #include "kernels.h"
 #include "nccl_dl.h"
+#include "safetensors.h"
 
 using namespace cg;
 
@@ -681,6 +683,50 @@ int32_t cg_decoder_set_param(cg_decoder* D, const char* name, const cg_tensor* t
   auto it = D->params.find(name);
   if (it != D->params.end()) { release(it->second); it->second = const_cast<cg_tensor*>(t); }
   else D->params.emplace(name, const_cast<cg_tensor*>(t));
+  return CG_OK;
+}
+
+// Checkpoint file -> decoder parameters (catgrad-llm/examples/llama/main.rs:279-354 and the
+// expert stacking of :173-264).  Every tensor crosses the host link once, in the element type the
+// file stores (bf16 stays bf16).  Per-expert matrices "...mlp.experts.{e}.{proj}.weight" land
+// directly in slot e of the stacked "[E, rows, cols]" tensor the expert block reads, allocated
+// when the layer's first expert shows up: one pass, where the reference concatenates the experts
+// pairwise (quadratic copying).  Several files (shards) may be loaded one after another.
+int32_t cg_decoder_load_safetensors(cg_decoder* D, const char* path) {
+  if (!D || !path) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (D->finalized) return fail(c, CG_ERR_INVALID, "decoder: already finalized");
+  std::string why;
+  std::unique_ptr<cg_safetensors> f(st_open(path, &why));
+  if (!f) return fail(c, CG_ERR_INVALID, "safetensors: " + why);
+  for (const StEntry& e : f->entries) {
+    int layer = -1, expert = -1, used = 0;
+    char proj[32] = {0};
+    if (sscanf(e.name.c_str(), "model.layers.%d.mlp.experts.%d.%31[a-z_].weight%n", &layer, &expert, proj, &used) == 3 &&
+        used == (int)e.name.size()) {
+      if (e.dims.size() != 2 || expert < 0 || expert >= D->cfg.n_experts)
+        return fail(c, CG_ERR_SHAPE, "decoder: " + e.name + " is not a matrix of one of the configured experts");
+      const std::string stacked = "model.layers." + std::to_string(layer) + ".mlp.experts." + proj + ".weight";
+      auto it = D->params.find(stacked);
+      if (it == D->params.end()) {
+        int64_t d3[3] = {D->cfg.n_experts, e.dims[0], e.dims[1]};
+        cg_tensor* t = nullptr;
+        CG_TRY(new_tensor(c, CG_F32, ST_BF16, d3, 3, &t));
+        it = D->params.emplace(stacked, t).first;
+      }
+      cg_tensor* dst = it->second;
+      if (dst->rank != 3 || dst->dims[1] != e.dims[0] || dst->dims[2] != e.dims[1])
+        return fail(c, CG_ERR_SHAPE, "decoder: the experts of " + stacked + " differ in shape");
+      CG_TRY(st_upload_into_bf16(c, f.get(), e, dst, (int64_t)expert * e.dims[0] * e.dims[1]));
+      continue;
+    }
+    cg_tensor* t = nullptr;
+    CG_TRY(st_upload(c, f.get(), e, &t));
+    Hold h(t);
+    CG_TRY(cg_decoder_set_param(D, e.name.c_str(), t));
+  }
+  // the copies read the mapping, which goes away with `f`
+  CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
   return CG_OK;
 }
 

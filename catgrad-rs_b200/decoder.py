@@ -41,6 +41,7 @@ class Decoder:
             ("cg_decoder_destroy", [vp]),
             ("cg_decoder_set_param", [vp, C.c_char_p, vp]),
             ("cg_decoder_finalize", [vp]),
+            ("cg_decoder_load_safetensors", [vp, C.c_char_p]),
             ("cg_decoder_reset", [vp]),
             ("cg_decoder_prefill", [vp, vp, out]),
             ("cg_decoder_decode", [vp, i32, out]),
@@ -134,6 +135,12 @@ class Decoder:
                 t = self.B.randn(shape, (seed << 32) ^ zlib.crc32(name.encode()), std=std)
             self.set_param(name, t)
             del t
+        self.finalize()
+
+    def load_file(self, *paths: str):
+        """Hand over every tensor of one or more .safetensors files (shards) and finalize."""
+        for path in paths:
+            self.B._check(self.B._lib.cg_decoder_load_safetensors(self._h, path.encode()))
         self.finalize()
 
     def finalize(self):

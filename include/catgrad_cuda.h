@@ -296,6 +296,14 @@ int32_t cg_decoder_destroy(cg_decoder*);
  * splits on '.', examples/llama/main.rs:325), e.g. "model.layers.0.self_attn.q_proj.weight".
  * Full (unsharded) tensors are passed on every rank; the decoder keeps its shard. */
 int32_t cg_decoder_set_param(cg_decoder*, const char* name, const cg_tensor* t);
+/* Hand over every tensor of a .safetensors checkpoint file (replaces the host-side load of
+ * examples/llama/main.rs:279-354: there every tensor is widened to a host Vec<f32> first; here the
+ * file is memory-mapped and each tensor crosses the host link once in its stored element type,
+ * F32 or BF16, anything else is refused like the reference's loader does).  Per-expert matrices
+ * "model.layers.L.mlp.experts.E.{gate,up,down}_proj.weight" are placed directly into the stacked
+ * [n_experts, rows, cols] tensors the expert block reads (examples/llama/main.rs:173-264 builds
+ * those by repeated concatenation).  May be called once per shard file, before finalize. */
+int32_t cg_decoder_load_safetensors(cg_decoder*, const char* path);
 /* Build fused weights, rope tables, workspace and TMA descriptors.  Call once after all
  * parameters are set. */
 int32_t cg_decoder_finalize(cg_decoder*);
@@ -340,6 +348,21 @@ int32_t cg_trace_read(cg_ctx*, uint64_t* out, int32_t slots);
  * attention, o GEMM, gate/up GEMM, down GEMM, then the LM head; next step likewise): when the
  * phase's grid barrier let the CTA through, and when the CTA finished its part of the phase. */
 int32_t cg_decoder_resident_trace(cg_decoder*, int32_t cta, uint64_t* out, int32_t n);
+
+/* --- .safetensors checkpoint files (examples/llama/main.rs:296-330 reads them through the
+ * safetensors and memmap2 crates).  cg_safetensors_open memory-maps the file and parses its
+ * header on the host (no device needed); cg_safetensors_tensor uploads tensor i as a tensor of the
+ * context: F32 data as cg_ndarray_from_vec_f32 would, BF16 data without widening on the host
+ * (kept as bf16 storage for rank >= 2 in a bf16-precision context, widened on the device
+ * otherwise).  `storage` in cg_safetensors_info: 0 = F32, 2 = BF16.  On failure
+ * cg_safetensors_open writes the reason to `err` (optional). --- */
+typedef struct cg_safetensors cg_safetensors;
+int32_t cg_safetensors_open(const char* path, cg_safetensors** out, char* err, int64_t err_cap);
+int32_t cg_safetensors_close(cg_safetensors*);
+int64_t cg_safetensors_count(const cg_safetensors*);
+int32_t cg_safetensors_info(const cg_safetensors*, int64_t i, const char** name, int32_t* storage, int32_t* rank,
+                            int64_t dims[CG_MAX_RANK]);
+int32_t cg_safetensors_tensor(cg_ctx*, const cg_safetensors*, int64_t i, cg_tensor** out);
 
 /* Row-wise arg-max for callers that cannot allocate device memory (code that runs while
  * another stream of the process is being captured into a CUDA graph, plugins with a fixed memory
