@@ -336,6 +336,7 @@ class CudaBackend(TraitBackend):
             ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
             ("cg_randn", [vp, _c_i64p, i32, C.c_uint64, f32, f32, out], i32),
             ("cg_probe_wait_timeout", [vp], i32),
+            ("cg_rope_tables", [vp, f32, i32, f32, f32, f32, f32, f32, i32, i64, i64, out, out], i32),
         ]:
             fn = getattr(L, name)
             fn.argtypes = args
@@ -362,6 +363,18 @@ class CudaBackend(TraitBackend):
 
     def set_option(self, name: str, value: int):
         self._check(self._lib.cg_set_option(self._ctx, name.encode(), int(value)))
+
+    def rope_tables(self, theta, seq_len, head_dim, scaling: dict | None = None):
+        """(cos, sin) [T, d/2] as the decoder builds them; `scaling` is a checkpoint's
+        rope_scaling dict ("llama3" or "yarn") or None for the plain formula."""
+        rs = scaling or {}
+        kind = {None: 0, "llama3": 1, "yarn": 2}[rs.get("rope_type", rs.get("type"))]
+        a, b = _c_vp(), _c_vp()
+        self._check(self._lib.cg_rope_tables(
+            self._ctx, float(theta), kind, float(rs.get("factor", 1.0)), float(rs.get("low_freq_factor", 1.0)),
+            float(rs.get("high_freq_factor", 4.0)), float(rs.get("beta_fast", 32.0)), float(rs.get("beta_slow", 1.0)),
+            int(rs.get("original_max_position_embeddings", 0)), int(seq_len), int(head_dim), C.byref(a), C.byref(b)))
+        return self._wrap(a), self._wrap(b)
 
     def probe_wait_timeout(self):
         """Enqueue the failure-path probe: a bounded wait on a flag nothing raises."""

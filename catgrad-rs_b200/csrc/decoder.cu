@@ -865,7 +865,11 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
   int64_t td[2] = {cfg.max_seq, d / 2};
   CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->cos_t));
   CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->sin_t));
-  CG_TRY(k_launch_rope_tables(c, cfg.rope_theta, cfg.max_seq, d, (float*)D->cos_t->data(), (float*)D->sin_t->data()));
+  RopeScaling rs;
+  rs.kind = cfg.rope_scaling; rs.factor = cfg.rope_factor; rs.low_freq_factor = cfg.rope_low_freq_factor;
+  rs.high_freq_factor = cfg.rope_high_freq_factor; rs.beta_fast = cfg.rope_beta_fast; rs.beta_slow = cfg.rope_beta_slow;
+  rs.original_max_pos = cfg.rope_original_max_pos;
+  CG_TRY(k_launch_rope_tables_scaled(c, cfg.rope_theta, rs, cfg.max_seq, d, (float*)D->cos_t->data(), (float*)D->sin_t->data()));
   if (cfg.rope_local_theta > 0.f && cfg.rope_local_every > 0) {
     CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->cos_l));
     CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &D->sin_l));

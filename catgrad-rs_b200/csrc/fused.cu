@@ -245,6 +245,44 @@ __global__ void k_rope_tables(float theta, int64_t T, int64_t half, float two_ov
   }
 }
 
+// Scaled variants (legacy/nn/rope.rs:32-201), every step in f32 and un-fused so that the table
+// equals an f32 evaluation of the reference's expression tree operation by operation.
+__global__ void k_rope_tables_scaled(float theta, RopeScaling rs, float yarn_low, float yarn_high, float mscale, int64_t T,
+                                     int64_t half, float two_over_d, float* cos_t, float* sin_t) {
+  const int64_t n = T * half;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t pos = i / half, j = i - pos * half;
+    const float f = __fmul_rn((float)j, two_over_d);
+    const float freq = (float)pow((double)theta, (double)f);
+    float inv = __fdiv_rn(1.0f, freq);
+    if (rs.kind == 1) {
+      // rope.rs:49-93
+      const float old_ctx = (float)rs.original_max_pos;
+      const float low_wl = __fdiv_rn(old_ctx, rs.low_freq_factor), high_wl = __fdiv_rn(old_ctx, rs.high_freq_factor);
+      const float wavelen = __fdiv_rn(6.2831855f, inv);  // 2 * PI in f32
+      const bool low = wavelen > low_wl;
+      const float inv1 = low ? __fdiv_rn(inv, rs.factor) : inv;
+      const bool high = wavelen < high_wl;
+      const float smooth = __fdiv_rn(__fsub_rn(__fdiv_rn(old_ctx, wavelen), rs.low_freq_factor),
+                                     __fsub_rn(rs.high_freq_factor, rs.low_freq_factor));
+      const float smoothed = __fadd_rn(__fmul_rn(smooth, inv1), __fdiv_rn(__fmul_rn(__fsub_rn(1.0f, smooth), inv1), rs.factor));
+      inv = (!high && !low) ? smoothed : inv1;
+    } else if (rs.kind == 2) {
+      // rope.rs:139-185: ramp = clamp((j - low) / (high - low), 0, 1); extrapolation share = 1 - ramp
+      float r = __fdiv_rn(__fsub_rn((float)j, yarn_low), __fsub_rn(yarn_high, yarn_low));
+      r = fminf(fmaxf(r, 0.0f), 1.0f);
+      const float ext = __fsub_rn(1.0f, r);
+      const float interp = __fdiv_rn(inv, rs.factor);
+      inv = __fadd_rn(__fmul_rn(interp, __fsub_rn(1.0f, ext)), __fmul_rn(inv, ext));
+    }
+    const float ang = __fmul_rn((float)pos, inv);
+    float cs = (float)cos((double)ang), sn = (float)sin((double)ang);
+    if (rs.kind == 2) { cs = __fmul_rn(cs, mscale); sn = __fmul_rn(sn, mscale); }
+    cos_t[i] = cs;
+    sin_t[i] = sn;
+  }
+}
+
 // x [rows, S, d] -> cos * x + sin * rotate_half(x), position pos0 + s
 __global__ void k_rope_apply(const float* x, const float* cos_t, const float* sin_t, int64_t S, int64_t d, int64_t pos0,
                              int64_t n, float* out) {
@@ -579,6 +617,28 @@ int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* co
   return CG_OK;
 }
 
+int k_launch_rope_tables_scaled(cg_ctx* c, float theta, const RopeScaling& rs, int64_t T, int64_t d, float* cos_t, float* sin_t) {
+  if (rs.kind == 0) return k_launch_rope_tables(c, theta, T, d, cos_t, sin_t);
+  if (rs.kind != 1 && rs.kind != 2) return fail(c, CG_ERR_INVALID, "rope scaling: kind must be 0 (none), 1 (llama3) or 2 (yarn)");
+  if (rs.factor <= 0.f || rs.original_max_pos <= 0) return fail(c, CG_ERR_INVALID, "rope scaling: factor and original_max_pos must be positive");
+  if (rs.kind == 1 && rs.high_freq_factor == rs.low_freq_factor) return fail(c, CG_ERR_INVALID, "rope scaling: high and low frequency factors coincide");
+  const int64_t n = T * (d / 2);
+  if (n == 0) return CG_OK;
+  float low = 0.f, high = 1.f, mscale = 1.f;
+  if (rs.kind == 2) {
+    // find_correction_range and rope_yarn_get_mscale (rope.rs:100-128), in f32 like the reference
+    const float two_pi = 2.0f * 3.14159265358979323846f;
+    auto corr = [&](float rot) { return ((float)d * logf((float)rs.original_max_pos / (rot * two_pi))) / (2.f * logf(theta)); };
+    low = corr(rs.beta_fast);
+    high = corr(rs.beta_slow);
+    if (high == low) return fail(c, CG_ERR_INVALID, "rope scaling: empty yarn correction range");
+    mscale = rs.factor <= 1.0f ? 1.0f : 0.1f * logf(rs.factor) + 1.0f;
+  }
+  k_rope_tables_scaled<<<grid_for(n, 256), 256, 0, c->core->stream>>>(theta, rs, low, high, mscale, T, d / 2, 2.0f / (float)d, cos_t, sin_t);
+  CG_LAUNCHED(c);
+  return CG_OK;
+}
+
 int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
   const int64_t warps = a.M * (a.nh + 2 * a.nkv);
   if (warps == 0) return CG_OK;
@@ -806,5 +866,22 @@ extern "C" int32_t cg_probe_wait_timeout(cg_ctx* c) {
   if (!c) return CG_ERR_INVALID;
   cg::k_probe_wait<<<1, 1, 0, c->core->stream>>>(c->core->dev_err);
   CG_LAUNCHED(c);
+  return CG_OK;
+}
+
+extern "C" int32_t cg_rope_tables(cg_ctx* c, float theta, int32_t kind, float factor, float low_freq_factor, float high_freq_factor,
+                                  float beta_fast, float beta_slow, int32_t original_max_pos, int64_t T, int64_t d,
+                                  cg_tensor** cos_out, cg_tensor** sin_out) {
+  if (!c || !cos_out || !sin_out || T < 0 || d < 2 || d % 2) return fail(c, CG_ERR_INVALID, "rope tables: bad argument");
+  RopeScaling rs;
+  rs.kind = kind; rs.factor = factor; rs.low_freq_factor = low_freq_factor; rs.high_freq_factor = high_freq_factor;
+  rs.beta_fast = beta_fast; rs.beta_slow = beta_slow; rs.original_max_pos = original_max_pos;
+  int64_t td[2] = {T, d / 2};
+  Hold ct, sn;
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &ct.t));
+  CG_TRY(new_tensor(c, CG_F32, ST_F32, td, 2, &sn.t));
+  CG_TRY(k_launch_rope_tables_scaled(c, theta, rs, T, d, (float*)ct.t->data(), (float*)sn.t->data()));
+  *cos_out = ct.take();
+  *sin_out = sn.take();
   return CG_OK;
 }

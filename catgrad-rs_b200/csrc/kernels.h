@@ -37,6 +37,16 @@ int k_launch_act_mul(cg_ctx* c, const float* gu, int64_t M, int64_t F, int act, 
 
 // Rotary tables exactly as the reference builds them: cos/sin [T, d/2] f32.
 int k_launch_rope_tables(cg_ctx* c, float theta, int64_t T, int64_t d, float* cos_t, float* sin_t);
+// The same with the frequency rescaling of long-context checkpoints
+// (catgrad-llm/src/legacy/nn/rope.rs:32-201): kind 1 = "llama3" (low frequencies divided by
+// `factor`, a smooth blend between the two wavelength thresholds), kind 2 = "yarn" (linear ramp
+// between interpolated and extrapolated frequencies, tables scaled by 0.1 ln(factor) + 1).
+struct RopeScaling {
+  int kind = 0;  // 0 none, 1 llama3, 2 yarn
+  float factor = 1.f, low_freq_factor = 1.f, high_freq_factor = 4.f, beta_fast = 32.f, beta_slow = 1.f;
+  int original_max_pos = 0;
+};
+int k_launch_rope_tables_scaled(cg_ctx* c, float theta, const RopeScaling& rs, int64_t T, int64_t d, float* cos_t, float* sin_t);
 
 struct RopeStoreArgs {
   const float* qkv;        // [M, (nh + 2 nkv) d]

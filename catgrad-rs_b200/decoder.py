@@ -23,6 +23,9 @@ class DecoderConfig(C.Structure):
         ("qk_norm", C.c_int32), ("act", C.c_int32), ("norm_plus_one", C.c_int32), ("post_norms", C.c_int32),
         ("embed_scale", C.c_float), ("attn_softcap", C.c_float), ("final_softcap", C.c_float),
         ("sliding_window", C.c_int32), ("window_every", C.c_int32),
+        ("rope_scaling", C.c_int32), ("rope_factor", C.c_float), ("rope_low_freq_factor", C.c_float),
+        ("rope_high_freq_factor", C.c_float), ("rope_beta_fast", C.c_float), ("rope_beta_slow", C.c_float),
+        ("rope_original_max_pos", C.c_int32),
         ("rope_local_theta", C.c_float), ("rope_local_every", C.c_int32),
         ("n_experts", C.c_int32), ("top_k", C.c_int32), ("moe_ffn", C.c_int32), ("norm_topk", C.c_int32),
         ("tp_rank", C.c_int32), ("tp_world", C.c_int32),
@@ -69,6 +72,17 @@ class Decoder:
         c.max_batch = max_batch
         c.tp_rank = tp_rank
         c.tp_world = tp_world
+        rs = getattr(cfg, "rope_scaling", None)
+        if rs:
+            # {"rope_type": "llama3" | "yarn", "factor": ..., ...} as in a checkpoint's config.json
+            kind = {"llama3": 1, "yarn": 2}[rs.get("rope_type", rs.get("type"))]
+            c.rope_scaling = kind
+            c.rope_factor = rs["factor"]
+            c.rope_low_freq_factor = rs.get("low_freq_factor", 1.0)
+            c.rope_high_freq_factor = rs.get("high_freq_factor", 4.0)
+            c.rope_beta_fast = rs.get("beta_fast", 32.0)
+            c.rope_beta_slow = rs.get("beta_slow", 1.0)
+            c.rope_original_max_pos = rs["original_max_position_embeddings"]
         arch = getattr(cfg, "arch", "llama")
         if arch == "qwen3":
             c.arch = 1

@@ -35,6 +35,13 @@ pub struct DecoderConfig {
     pub final_softcap: f32,
     pub sliding_window: i32,
     pub window_every: i32,
+    pub rope_scaling: i32,
+    pub rope_factor: f32,
+    pub rope_low_freq_factor: f32,
+    pub rope_high_freq_factor: f32,
+    pub rope_beta_fast: f32,
+    pub rope_beta_slow: f32,
+    pub rope_original_max_pos: i32,
     pub rope_local_theta: f32,
     pub rope_local_every: i32,
     pub n_experts: i32,

@@ -45,6 +45,10 @@ class ModelConfig:
     # rope_local_base_freq, the others with rope_theta (0 = one base everywhere)
     sliding_window_pattern: int = 0
     rope_local_base_freq: float = 0.0
+    # frequency rescaling of long-context checkpoints (legacy/models/utils.rs:19-48), e.g.
+    # {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+    #  "original_max_position_embeddings": 8192}
+    rope_scaling: dict | None = None
     extras: dict = field(default_factory=dict)
 
     def __post_init__(self):

@@ -273,6 +273,14 @@ typedef struct cg_decoder_config {
   float final_softcap;
   int32_t sliding_window;   /* 0 = none */
   int32_t window_every;     /* layers with (i % window_every) != window_every-1 use the window */
+  /* frequency rescaling of long-context checkpoints (legacy/nn/rope.rs:32-201; legacy/models/utils.rs:19-48) */
+  int32_t rope_scaling;     /* 0 = none, 1 = "llama3", 2 = "yarn" */
+  float rope_factor;
+  float rope_low_freq_factor;   /* llama3 */
+  float rope_high_freq_factor;  /* llama3 */
+  float rope_beta_fast;         /* yarn */
+  float rope_beta_slow;         /* yarn */
+  int32_t rope_original_max_pos;
   float rope_local_theta;   /* 0 = one rope base; else the base of "local" layers (gemma3.rs:154-159) */
   int32_t rope_local_every; /* layers with (i + 1) % rope_local_every != 0 rotate with rope_local_theta,
                                the others with rope_theta (the reference's sliding_window_pattern) */
@@ -341,6 +349,13 @@ int32_t cg_decoder_time_gemms(cg_decoder*, int32_t batch, int32_t iters, float* 
  * ready, last CTA finished.  cg_trace_read copies `slots` x 4 values. */
 int32_t cg_trace_enable(cg_ctx*, int32_t on);
 int32_t cg_trace_read(cg_ctx*, uint64_t* out, int32_t slots);
+
+/* Rotary tables cos, sin [T, d/2] as the runner builds them: the plain formula of
+ * catgrad-llm/src/helpers.rs:164-193 (kind 0) or with the "llama3" (kind 1) / "yarn" (kind 2)
+ * frequency rescaling of catgrad-llm/src/legacy/nn/rope.rs:32-201.  Unused factors are ignored. */
+int32_t cg_rope_tables(cg_ctx*, float theta, int32_t kind, float factor, float low_freq_factor, float high_freq_factor,
+                       float beta_fast, float beta_slow, int32_t original_max_pos, int64_t T, int64_t d,
+                       cg_tensor** cos_out, cg_tensor** sin_out);
 
 /* Diagnostics of the resident decode kernel ("resident" option): out == NULL arms a timeline of
  * resident CTA `cta` for the next decode call (cta < 0 disarms); otherwise copies n globaltimer
