@@ -603,10 +603,18 @@ int try_resident(cg_decoder* D, int steps, bool* ran) {
   return CG_OK;
 }
 
+__global__ void k_set_state(int64_t* state, int64_t pos, int64_t generated) {
+  state[0] = pos;
+  state[1] = generated;
+}
+
+// The device copy of {position, tokens generated}, set in stream order by a one-thread kernel:
+// no host buffer is involved, so nothing has to be waited for.
 int set_state(cg_decoder* D, int64_t pos, int64_t generated) {
-  int64_t v[2] = {pos, generated};
-  CG_CUDA(D->c, cudaMemcpyAsync(D->state->data(), v, 16, cudaMemcpyHostToDevice, D->c->core->stream));
-  CG_CUDA(D->c, cudaStreamSynchronize(D->c->core->stream));  // `v` is on the stack
+  k_set_state<<<1, 1, 0, D->c->core->stream>>>((int64_t*)D->state->data(), pos, generated);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(D->c, e, "k_set_state");
+  D->c->launches++;
   D->pos = pos;
   D->generated = generated;
   return CG_OK;
@@ -909,16 +917,22 @@ int32_t cg_decoder_reset(cg_decoder* D) {
   return set_state(D, 0, 0);
 }
 
-int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
-  if (!D || !tokens) return CG_ERR_INVALID;
+}  // extern "C"
+
+namespace {
+
+// Runs `tokens` [B, S] through the model at cache positions [base, base + S), appends their keys
+// and values, and leaves the greedy next token of every row in the token buffer (counted as
+// generated token number `generated`).
+int prefill_at(cg_decoder* D, const cg_tensor* tokens, int64_t base, int64_t generated, cg_tensor** logits_out) {
   cg_ctx* c = D->c;
-  if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
   if (tokens->tag != CG_U32 || tokens->rank != 2) return fail(c, CG_ERR_SHAPE, "decoder: tokens must be U32 [B, S]");
   const int64_t B = tokens->dims[0], S = tokens->dims[1];
-  if (B < 1 || B > D->cfg.max_batch || S < 1 || S > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: batch or length out of range");
+  if (B < 1 || B > D->cfg.max_batch || S < 1 || base + S > D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: batch or length out of range");
+  if (generated >= D->cfg.max_seq) return fail(c, CG_ERR_SHAPE, "decoder: token history is full");
   Hold tk;
   CG_TRY(as_contiguous(c, tokens, &tk.t));
-  CG_TRY(set_state(D, 0, 0));
+  CG_TRY(set_state(D, base, generated));
   D->B = B;
   // the prompt is processed in position chunks so the workspace stays bounded
   const int64_t chunk_tokens = c->opt_prefill_chunk;
@@ -931,20 +945,49 @@ int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** l
     CG_TRY(k_launch_embed(c, (const uint32_t*)tk.t->data(), S, p0, s, D->embed->data(), D->embed->storage, D->cfg.vocab,
                           B * s, D->H, D->cfg.embed_scale > 0.f ? D->cfg.embed_scale : 1.f, (float*)D->x->data()));
     // a one-token chunk would take the decode attention path, which reads the device position
-    if (s == 1) CG_TRY(set_state(D, p0, 0));
-    CG_TRY(run_layers(D, B, s, p0, s == 1));
+    if (s == 1) CG_TRY(set_state(D, base + p0, generated));
+    CG_TRY(run_layers(D, B, s, base + p0, s == 1));
     if (p0 + s == S) {
-      CG_TRY(set_state(D, S, 0));
+      CG_TRY(set_state(D, base + S, generated));
       CG_TRY(run_head(D, B, s, false));
-      // count the prefill's token: generated = 1 (position stays S: that token is not cached yet)
-      int64_t v[2] = {S, 1};
-      CG_CUDA(c, cudaMemcpyAsync(D->state->data(), v, 16, cudaMemcpyHostToDevice, c->core->stream));
-      CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
-      D->pos = S;
-      D->generated = 1;
+      // count the new token (the position stays base + S: that token is not cached yet)
+      CG_TRY(set_state(D, base + S, generated + 1));
     }
   }
   return logits_copy(D, logits_out);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  if (!D || !tokens) return CG_ERR_INVALID;
+  if (!D->finalized) return fail(D->c, CG_ERR_INVALID, "decoder: finalize first");
+  return prefill_at(D, tokens, 0, 0, logits_out);
+}
+
+int32_t cg_decoder_append(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  if (!D || !tokens) return CG_ERR_INVALID;
+  cg_ctx* c = D->c;
+  if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
+  if (D->B == 0) return prefill_at(D, tokens, 0, 0, logits_out);  // nothing cached yet
+  if (tokens->rank != 2 || tokens->dims[0] != D->B) return fail(c, CG_ERR_SHAPE, "decoder: append needs the cached batch size");
+  return prefill_at(D, tokens, D->pos, D->generated, logits_out);
+}
+
+int32_t cg_decoder_truncate(cg_decoder* D, int64_t positions) {
+  if (!D || !D->finalized) return CG_ERR_INVALID;
+  if (positions < 0 || positions > D->pos) return fail(D->c, CG_ERR_INVALID, "decoder: cannot truncate to more positions than are cached");
+  if (positions == 0) D->B = 0;
+  return set_state(D, positions, 0);
+}
+
+int32_t cg_decoder_position(cg_decoder* D, int64_t* cached, int64_t* generated) {
+  if (!D) return CG_ERR_INVALID;
+  if (cached) *cached = D->pos;
+  if (generated) *generated = D->generated;
+  return CG_OK;
 }
 
 int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) {

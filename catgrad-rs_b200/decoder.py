@@ -47,6 +47,9 @@ class Decoder:
             ("cg_decoder_load_safetensors", [vp, C.c_char_p]),
             ("cg_decoder_reset", [vp]),
             ("cg_decoder_prefill", [vp, vp, out]),
+            ("cg_decoder_append", [vp, vp, out]),
+            ("cg_decoder_truncate", [vp, C.c_int64]),
+            ("cg_decoder_position", [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
             ("cg_decoder_decode", [vp, i32, out]),
             ("cg_decoder_step_with", [vp, vp, out]),
             ("cg_decoder_tokens", [vp, out]),
@@ -173,6 +176,20 @@ class Decoder:
 
     def prefill(self, tokens: TaggedTensor, want_logits=False):
         return self._maybe_logits(self.B._lib.cg_decoder_prefill, tokens._h, want_logits=want_logits)
+
+    def append(self, tokens: TaggedTensor, want_logits=False):
+        """Run [B, S] more tokens on top of the cached positions."""
+        return self._maybe_logits(self.B._lib.cg_decoder_append, tokens._h, want_logits=want_logits)
+
+    def truncate(self, positions: int):
+        """Forget the cached positions from `positions` on."""
+        self.B._check(self.B._lib.cg_decoder_truncate(self._h, int(positions)))
+
+    def position(self):
+        """(cached positions, tokens generated since the last prefill / truncate)"""
+        a, b = C.c_int64(), C.c_int64()
+        self.B._check(self.B._lib.cg_decoder_position(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
 
     def decode(self, steps: int, want_logits=False):
         return self._maybe_logits(self.B._lib.cg_decoder_decode, int(steps), want_logits=want_logits)

@@ -6,4 +6,4 @@ order, that the cited reference function lowers to.  They work on any object wit
 trait's methods (catgrad/src/interpreter/backend/mod.rs:22-82), so the same stream drives
 the CUDA backend and a checker.
 """
-from . import nn, helpers, llama, qwen3, gemma, gpt2, granite, deepseek  # noqa: F401
+from . import nn, helpers, llama, qwen3, gemma, gpt2, granite, deepseek, llama_kv  # noqa: F401

@@ -321,6 +321,17 @@ int32_t cg_decoder_reset(cg_decoder*);
  * [0, S) and leaves the greedy next token of every row in the decoder's token buffer.
  * If logits_out != NULL it receives an F32 tensor [B, V] with the last position's logits. */
 int32_t cg_decoder_prefill(cg_decoder*, const cg_tensor* tokens, cg_tensor** logits_out);
+/* Continue a cached sequence: tokens is a DEVICE U32 tensor [B, S] (B as cached) that is run at
+ * cache positions [cached, cached + S) on top of what prefill / decode / earlier appends left,
+ * and the greedy next token of every row is left in the token buffer (as after prefill).  With
+ * cg_decoder_truncate this is the prefix reuse of the reference's serving runner
+ * (catgrad-llm/src/run.rs:282-305 keeps its KV cache when the new context extends the old one;
+ * here any common prefix is kept).  cg_decoder_truncate forgets the cached positions from
+ * `positions` on and clears the record of generated tokens; cg_decoder_position reports how many
+ * positions are cached and how many tokens have been generated since the last prefill/truncate. */
+int32_t cg_decoder_append(cg_decoder*, const cg_tensor* tokens, cg_tensor** logits_out);
+int32_t cg_decoder_truncate(cg_decoder*, int64_t positions);
+int32_t cg_decoder_position(cg_decoder*, int64_t* cached, int64_t* generated);
 /* Advance every row by `steps` greedy tokens, feeding each step's argmax to the next with
  * no host round trip.  If logits_out != NULL, receives the last step's logits [B, V]. */
 int32_t cg_decoder_decode(cg_decoder*, int32_t steps, cg_tensor** logits_out);
