@@ -237,6 +237,39 @@ __global__ void k_reduce_rows(const void* x, int st, int isf, uint32_t* out, int
   }
 }
 
+// arg-max of each row of a contiguous f32 [rows, n], n a multiple of 4, rows 16-byte aligned:
+// 128-bit loads, and the running maximum kept as a 32-bit total-order key plus an index (a later
+// index wins ties, and every thread meets its elements in ascending index order, so `>=` keeps
+// the last one); the 64-bit (key, index) pairs only meet in the final merges.
+__global__ void k_argmax_rows_f32(const float* x, uint32_t* out, int64_t n) {
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  __shared__ unsigned long long sh64[32];
+  const uint4* r4 = (const uint4*)(x + row * n);
+  const int n4 = (int)(n / 4);
+  uint32_t bk = 0, bi = 0;
+  bool any = false;
+  for (int i = tid; i < n4; i += blockDim.x) {
+    const uint4 v = r4[i];
+    const uint32_t k0 = total_key(v.x), k1 = total_key(v.y), k2 = total_key(v.z), k3 = total_key(v.w);
+    // the last of the four that attains their maximum
+    uint32_t k = k0, j = 0;
+    if (k1 >= k) { k = k1; j = 1; }
+    if (k2 >= k) { k = k2; j = 2; }
+    if (k3 >= k) { k = k3; j = 3; }
+    if (!any || k >= bk) { bk = k; bi = (uint32_t)i * 4u + j; any = true; }
+  }
+  unsigned long long best = any ? (((unsigned long long)bk << 32) | bi) : 0ull;
+  best = warp_max_u64(best);
+  if (lane == 0) sh64[wid] = best;
+  __syncthreads();
+  if (wid == 0) {
+    best = lane < nw ? sh64[lane] : 0ull;
+    best = warp_max_u64(best);
+    if (lane == 0) out[row] = (uint32_t)(best & 0xFFFFFFFFull);
+  }
+}
+
 // top-k of each row of a contiguous f32 [rows, n]: k rounds of "largest key below the last
 // one taken", key = (total order key << 32) | ~index, so equal values come out in
 // ascending index order like a stable descending sort.
@@ -287,6 +320,20 @@ __global__ void k_index(const uint32_t* x, const uint32_t* idx, uint32_t* out, i
     uint32_t r = idx[j];
     if (r >= xd) { *err = DEV_INDEX; r = 0; }
     out[i] = x[(o * xd + r) * inner + in];
+  }
+}
+// The same when a gathered row (`inner` elements) is a whole number of 16-byte vectors: one block
+// per output row copies it with 128-bit loads and stores; no per-element index arithmetic.
+// row_vecs = bytes of a row / 16.
+__global__ void k_index_rows(const uint4* x, const uint32_t* idx, uint4* out, int64_t xd, int64_t ni, int64_t rows,
+                             int64_t row_vecs, int32_t* err) {
+  for (int64_t t = blockIdx.x; t < rows; t += gridDim.x) {
+    const int64_t j = t % ni, o = t / ni;
+    uint32_t r = idx[j];
+    if (r >= xd) { if (threadIdx.x == 0) *err = DEV_INDEX; r = 0; }
+    const uint4* src = x + (o * xd + r) * row_vecs;
+    uint4* dst = out + t * row_vecs;
+    for (int64_t i = threadIdx.x; i < row_vecs; i += blockDim.x) dst[i] = src[i];
   }
 }
 // same for 2-byte elements
@@ -537,8 +584,11 @@ static int reduce(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
   if (rows) {
     if (rows > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "too many rows");
     const int block = n >= 1024 ? 256 : (n >= 128 ? 128 : 32);
-    k_reduce_rows<RED><<<(unsigned)rows, block, 0, c->core->stream>>>(xc.t->data(), xc.t->storage, x->tag == CG_F32,
-                                                                     (uint32_t*)r.t->data(), n);
+    if (RED == RED_ARGMAX && x->tag == CG_F32 && xc.t->storage == ST_F32 && (n & 3) == 0 && (((uintptr_t)xc.t->data()) & 15) == 0)
+      k_argmax_rows_f32<<<(unsigned)rows, block, 0, c->core->stream>>>((const float*)xc.t->data(), (uint32_t*)r.t->data(), n);
+    else
+      k_reduce_rows<RED><<<(unsigned)rows, block, 0, c->core->stream>>>(xc.t->data(), xc.t->storage, x->tag == CG_F32,
+                                                                       (uint32_t*)r.t->data(), n);
     CG_LAUNCHED(c);
   }
   *out = r.take();
@@ -763,7 +813,15 @@ int32_t cg_index(cg_ctx* c, const cg_tensor* x, int32_t dim, const cg_tensor* in
   const int64_t n = r.t->numel();
   if (n) {
     if (x->dims[dim] == 0) return fail(c, CG_ERR_INDEX, "index out of bounds");
-    if (x->storage == ST_BF16)
+    const int64_t row_bytes = inner * (int64_t)storage_bytes(x->storage);
+    const bool rows_vec = row_bytes >= 256 && row_bytes % 16 == 0 && ((((uintptr_t)xc.t->data()) | ((uintptr_t)r.t->data())) & 15) == 0;
+    if (rows_vec) {
+      const int64_t rows = outer * ni;
+      const int block = row_bytes / 16 >= 256 ? 256 : (row_bytes / 16 >= 64 ? 64 : 32);
+      k_index_rows<<<(unsigned)std::min<int64_t>(rows, 148 * 64), block, 0, c->core->stream>>>(
+          (const uint4*)xc.t->data(), (const uint32_t*)ic.t->data(), (uint4*)r.t->data(), x->dims[dim], ni, rows, row_bytes / 16,
+          c->core->dev_err);
+    } else if (x->storage == ST_BF16)
       k_index16<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const uint16_t*)xc.t->data(), (const uint32_t*)ic.t->data(),
                                                               (uint16_t*)r.t->data(), outer, x->dims[dim], ni, inner,
                                                               c->core->dev_err);

@@ -75,6 +75,43 @@ __global__ void k_rmsnorm(const float* x, int64_t ldx, const float* gamma, float
   const float* row = x + m * ldx;
   float ss = 0.f;
   const bool vec = (H % 4 == 0) && (ldx % 4 == 0) && (((uintptr_t)x & 15) == 0);
+  if (vec && H <= (int64_t)blockDim.x * 16 && (((uintptr_t)gamma & 15) == 0) && (((uintptr_t)out & 15) == 0)) {
+    // The row fits the block's registers (up to four 128-bit loads per thread, all issued before
+    // the first use): one pass over HBM, no second read of the row.
+    const float4* r4 = (const float4*)row;
+    const int n4 = (int)(H / 4);
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      v[j] = i < n4 ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    ss = block_sum(ss, sh);
+    const float rms = sqrtf(ss / (float)H + eps);
+    const float4* g4 = (const float4*)gamma;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i >= n4) break;
+      float4 g = g4[i];
+      if (plus_one) { g.x += 1.f; g.y += 1.f; g.z += 1.f; g.w += 1.f; }
+      const float4 r = make_float4(v[j].x / rms * g.x, v[j].y / rms * g.y, v[j].z / rms * g.z, v[j].w / rms * g.w);
+      if (MODE == 0) {
+        ((float4*)((float*)out + m * H))[i] = r;
+      } else if (MODE == 1) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+        ((uint2*)((__nv_bfloat16*)out + m * H))[i] = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+      } else {
+        float4* o = (float4*)((float*)out + m * H) + i;
+        float4 a = *o;
+        a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
+        *o = a;
+      }
+    }
+    return;
+  }
   if (vec) {
     const float4* r4 = (const float4*)row;
     for (int64_t i = threadIdx.x; i < H / 4; i += blockDim.x) {
@@ -198,6 +235,23 @@ __global__ void k_act_mul(const float* gu, int64_t F, int act, __nv_bfloat16* ou
     out[m * F + i] = __float2bfloat16_rn(a * u[i]);
   }
 }
+// 128-bit loads and stores, two independent vectors per thread and pass
+__global__ void k_act_mul_f32_vec(const float4* g, const float4* u, int64_t n4, int act, float4* out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += 2 * stride) {
+    const int64_t k = i + stride;
+    const float4 a0 = g[i], b0 = u[i];
+    const bool two = k < n4;
+    const float4 a1 = two ? g[k] : a0, b1 = two ? u[k] : b0;
+    float4 r0, r1;
+    r0.x = (act == 0 ? silu_f(a0.x) : gelu_f(a0.x)) * b0.x; r0.y = (act == 0 ? silu_f(a0.y) : gelu_f(a0.y)) * b0.y;
+    r0.z = (act == 0 ? silu_f(a0.z) : gelu_f(a0.z)) * b0.z; r0.w = (act == 0 ? silu_f(a0.w) : gelu_f(a0.w)) * b0.w;
+    r1.x = (act == 0 ? silu_f(a1.x) : gelu_f(a1.x)) * b1.x; r1.y = (act == 0 ? silu_f(a1.y) : gelu_f(a1.y)) * b1.y;
+    r1.z = (act == 0 ? silu_f(a1.z) : gelu_f(a1.z)) * b1.z; r1.w = (act == 0 ? silu_f(a1.w) : gelu_f(a1.w)) * b1.w;
+    out[i] = r0;
+    if (two) out[k] = r1;
+  }
+}
 __global__ void k_act_mul_f32(const float* g, const float* u, int64_t n, int act, float* out) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float a = act == 0 ? silu_f(g[i]) : gelu_f(g[i]);
@@ -211,6 +265,40 @@ __global__ void k_softmax(const float* x, int64_t n, float softcap, float* out) 
   const float* row = x + (int64_t)blockIdx.x * n;
   float* o = out + (int64_t)blockIdx.x * n;
   float mx = -3.4028234663852886e38f;  // the reference folds max from f32::MIN
+  if ((n & 3) == 0 && n <= (int64_t)blockDim.x * 16 && (((uintptr_t)row & 15) == 0) && (((uintptr_t)o & 15) == 0)) {
+    // register-resident row: one read and one write of HBM per element
+    const float4* r4 = (const float4*)row;
+    const int n4 = (int)(n / 4);
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      const float4 t = i < n4 ? r4[i] : make_float4(mx, mx, mx, mx);
+      v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    if (softcap > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if ((int)threadIdx.x + (j >> 2) * (int)blockDim.x < n4) v[j] = softcap * tanh_f(v[j] / softcap);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) mx = fmaxf(mx, v[j]);
+    mx = block_max(mx, sh);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const bool live = (int)threadIdx.x + (j >> 2) * (int)blockDim.x < n4;
+      v[j] = live ? __expf(v[j] - mx) : 0.f;
+      s += v[j];
+    }
+    s = block_sum(s, sh);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) ((float4*)o)[i] = make_float4(v[4 * j] / s, v[4 * j + 1] / s, v[4 * j + 2] / s, v[4 * j + 3] / s);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
     float v = row[i];
     if (softcap > 0.f) v = softcap * tanh_f(v / softcap);
@@ -293,6 +381,23 @@ __global__ void k_rope_apply(const float* x, const float* cos_t, const float* si
     const float c = cos_t[(pos0 + s) * half + j], sn = sin_t[(pos0 + s) * half + j];
     const float rot = e < half ? -x[i + half] : x[i - half];
     out[i] = c * x[i] + sn * rot;
+  }
+}
+
+// Four rotation pairs per thread: 128-bit loads of both halves of the head and of the tables,
+// 128-bit stores.  x is [rows, S, d] with d / 2 a multiple of 4; n4 = rows * S * (d / 8) groups.
+__global__ void k_rope_apply_vec(const float* x, const float* cos_t, const float* sin_t, int64_t S, int64_t d, int64_t pos0,
+                                 int64_t n4, float* out) {
+  const int64_t half = d / 2, per_row = half / 4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row, j = (i - r * per_row) * 4;   // r = row * S + s
+    const int64_t s = r % S;
+    const float4 x1 = *(const float4*)(x + r * d + j), x2 = *(const float4*)(x + r * d + half + j);
+    const float4 c = *(const float4*)(cos_t + (pos0 + s) * half + j), sn = *(const float4*)(sin_t + (pos0 + s) * half + j);
+    *(float4*)(out + r * d + j) = make_float4(c.x * x1.x + sn.x * -x2.x, c.y * x1.y + sn.y * -x2.y, c.z * x1.z + sn.z * -x2.z,
+                                              c.w * x1.w + sn.w * -x2.w);
+    *(float4*)(out + r * d + half + j) = make_float4(c.x * x2.x + sn.x * x1.x, c.y * x2.y + sn.y * x1.y, c.z * x2.z + sn.z * x1.z,
+                                                     c.w * x2.w + sn.w * x1.w);
   }
 }
 
@@ -565,7 +670,8 @@ int k_launch_embed(cg_ctx* c, const uint32_t* tokens, int64_t tok_ld, int64_t to
 int k_launch_rmsnorm(cg_ctx* c, const float* x, int64_t ldx, const float* gamma, float eps, int plus_one, int64_t M,
                      int64_t H, void* out, int out_bf16) {
   if (M == 0) return CG_OK;
-  const int block = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  // (up to 16 elements per thread stay in registers: 256 threads for rows of 4096, 512 for 8192)
+  const int block = H > 4096 ? 512 : (H > 2048 ? 256 : 128);
   if (out_bf16) CG_CUDA(c, launch_kernel(c, k_rmsnorm<1>, dim3((unsigned)M), dim3(block), 0, 1, x, ldx, gamma, eps, plus_one, H, out));
   else CG_CUDA(c, launch_kernel(c, k_rmsnorm<0>, dim3((unsigned)M), dim3(block), 0, 1, x, ldx, gamma, eps, plus_one, H, out));
   CG_LAUNCHED(c);
@@ -745,7 +851,7 @@ int32_t cg_fused_softmax(cg_ctx* c, const cg_tensor* x, float softcap, cg_tensor
   const int64_t rows = n ? x->numel() / n : 0;
   if (rows > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "too many rows");
   if (rows) {
-    const int block = n >= 2048 ? 512 : (n >= 256 ? 256 : 64);
+    const int block = n > 4096 ? 512 : (n > 2048 ? 256 : (n >= 256 ? 128 : 64));
     k_softmax<<<(unsigned)rows, block, 0, c->core->stream>>>((const float*)xc.t->data(), n, softcap, (float*)r.t->data());
     CG_LAUNCHED(c);
   }
@@ -766,8 +872,13 @@ int32_t cg_fused_act_mul(cg_ctx* c, const cg_tensor* gate, const cg_tensor* up, 
   CG_TRY(new_tensor(c, CG_F32, ST_F32, gate->dims, gate->rank, &r.t));
   const int64_t n = r.t->numel();
   if (n) {
-    k_act_mul_f32<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)g.t->data(), (const float*)u.t->data(), n,
-                                                                act, (float*)r.t->data());
+    const bool aligned = ((((uintptr_t)g.t->data()) | ((uintptr_t)u.t->data()) | ((uintptr_t)r.t->data())) & 15) == 0;
+    if ((n & 3) == 0 && aligned)
+      k_act_mul_f32_vec<<<grid_for(n / 8 + 1, 256, 148 * 32), 256, 0, c->core->stream>>>(
+          (const float4*)g.t->data(), (const float4*)u.t->data(), n / 4, act, (float4*)r.t->data());
+    else
+      k_act_mul_f32<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)g.t->data(), (const float*)u.t->data(), n,
+                                                                  act, (float*)r.t->data());
     CG_LAUNCHED(c);
   }
   *out = r.take();
@@ -788,9 +899,14 @@ int32_t cg_fused_rope(cg_ctx* c, const cg_tensor* x, float theta, int64_t pos0, 
   CG_TRY(k_launch_rope_tables(c, theta, T, d, (float*)ct.t->data(), (float*)sn.t->data()));
   const int64_t n = r.t->numel();
   if (n) {
-    k_rope_apply<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)xc.t->data(), (const float*)ct.t->data(),
-                                                               (const float*)sn.t->data(), S, d, pos0, n,
-                                                               (float*)r.t->data());
+    const bool aligned = ((((uintptr_t)xc.t->data()) | ((uintptr_t)r.t->data()) | ((uintptr_t)ct.t->data()) | ((uintptr_t)sn.t->data())) & 15) == 0;
+    if (d % 8 == 0 && aligned)
+      k_rope_apply_vec<<<grid_for(n / 8, 256, 148 * 32), 256, 0, c->core->stream>>>(
+          (const float*)xc.t->data(), (const float*)ct.t->data(), (const float*)sn.t->data(), S, d, pos0, n / 8, (float*)r.t->data());
+    else
+      k_rope_apply<<<grid_for(n, 256), 256, 0, c->core->stream>>>((const float*)xc.t->data(), (const float*)ct.t->data(),
+                                                                 (const float*)sn.t->data(), S, d, pos0, n,
+                                                                 (float*)r.t->data());
     CG_LAUNCHED(c);
   }
   *out = r.take();
