@@ -336,6 +336,7 @@ class CudaBackend(TraitBackend):
             ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
             ("cg_randn", [vp, _c_i64p, i32, C.c_uint64, f32, f32, out], i32),
             ("cg_probe_wait_timeout", [vp], i32),
+            ("cg_lazy_stats", [vp, _c_i64p, _c_i64p, _c_i64p], i32),
             ("cg_rope_tables", [vp, f32, i32, f32, f32, f32, f32, f32, i32, i64, i64, out, out], i32),
         ]:
             fn = getattr(L, name)
@@ -375,6 +376,12 @@ class CudaBackend(TraitBackend):
             float(rs.get("high_freq_factor", 4.0)), float(rs.get("beta_fast", 32.0)), float(rs.get("beta_slow", 1.0)),
             int(rs.get("original_max_position_embeddings", 0)), int(seq_len), int(head_dim), C.byref(a), C.byref(b)))
         return self._wrap(a), self._wrap(b)
+
+    def lazy_stats(self):
+        """(trait calls recorded, chains fused, calls pending) of the deferred-evaluation mode."""
+        a, b, d = C.c_int64(), C.c_int64(), C.c_int64()
+        self._check(self._lib.cg_lazy_stats(self._ctx, C.byref(a), C.byref(b), C.byref(d)))
+        return a.value, b.value, d.value
 
     def probe_wait_timeout(self):
         """Enqueue the failure-path probe: a bounded wait on a flag nothing raises."""

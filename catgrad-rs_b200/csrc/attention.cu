@@ -249,6 +249,7 @@ using namespace cg;
 
 extern "C" int32_t cg_fused_attention(cg_ctx* c, const cg_tensor* q, const cg_tensor* k, const cg_tensor* v, int64_t window,
                                       float softcap, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !q || !k || !v || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (q->tag != CG_F32 || k->tag != CG_F32 || v->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "attention wants F32 tensors");
   if (q->rank != 4 || k->rank != 4 || v->rank != 4) return fail(c, CG_ERR_SHAPE, "attention wants [b, heads, s, d]");

@@ -308,11 +308,14 @@ int project_add(cg_decoder* D, const cg_tensor* xin, int64_t M, const cg_tensor*
   if (push) return gemm(D, xin, M, w, nullptr, nullptr, 3);
   if (!tp && !post_norm) return gemm(D, xin, M, w, x, x, 2);
   float* t = (float*)D->tmp->data();
-  if (tp && !post_norm && !small_m(M, D->H) && D->H % 2 == 0) {
+  if (tp && !post_norm && !small_m(M, D->H) && D->H % 2 == 0 && D->cfg.n_experts == 0) {
     // prefill: the partial products travel as bf16 (half the bytes of the f32 residual stream;
     // the all-reduce is bandwidth-bound at these sizes), and one pass adds the reduced rows to
     // the replicated f32 residual and writes the norm the next block starts with.  Every rank
     // receives the same reduced rows, so the residual stream stays bit-identical across ranks.
+    // Models with expert layers keep the f32 payload: a router sits behind the residual stream,
+    // and a bf16-sized perturbation can flip a near-tie in its top-k, which the parity contract
+    // (expert ids identical to the reference) does not allow.
     __nv_bfloat16* tb = (__nv_bfloat16*)D->tmp->data();
     CG_TRY(gemm(D, xin, M, w, tb, nullptr, 1));
     CG_TRY(all_reduce_bf16(D, tb, M * D->H));
@@ -685,6 +688,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
 }
 
 int32_t cg_decoder_set_param(cg_decoder* D, const char* name, const cg_tensor* t) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !name || !t) return CG_ERR_INVALID;
   if (D->finalized) return fail(D->c, CG_ERR_INVALID, "decoder: already finalized");
   const_cast<cg_tensor*>(t)->rc++;
@@ -701,6 +705,7 @@ int32_t cg_decoder_set_param(cg_decoder* D, const char* name, const cg_tensor* t
 // when the layer's first expert shows up: one pass, where the reference concatenates the experts
 // pairwise (quadratic copying).  Several files (shards) may be loaded one after another.
 int32_t cg_decoder_load_safetensors(cg_decoder* D, const char* path) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !path) return CG_ERR_INVALID;
   cg_ctx* c = D->c;
   if (D->finalized) return fail(c, CG_ERR_INVALID, "decoder: already finalized");
@@ -739,6 +744,7 @@ int32_t cg_decoder_load_safetensors(cg_decoder* D, const char* path) {
 }
 
 int32_t cg_decoder_finalize(cg_decoder* D) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D) return CG_ERR_INVALID;
   cg_ctx* c = D->c;
   if (D->finalized) return CG_OK;
@@ -962,12 +968,14 @@ int prefill_at(cg_decoder* D, const cg_tensor* tokens, int64_t base, int64_t gen
 extern "C" {
 
 int32_t cg_decoder_prefill(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !tokens) return CG_ERR_INVALID;
   if (!D->finalized) return fail(D->c, CG_ERR_INVALID, "decoder: finalize first");
   return prefill_at(D, tokens, 0, 0, logits_out);
 }
 
 int32_t cg_decoder_append(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !tokens) return CG_ERR_INVALID;
   cg_ctx* c = D->c;
   if (!D->finalized) return fail(c, CG_ERR_INVALID, "decoder: finalize first");
@@ -1037,6 +1045,7 @@ int32_t cg_decoder_decode(cg_decoder* D, int32_t steps, cg_tensor** logits_out) 
 }
 
 int32_t cg_decoder_step_with(cg_decoder* D, const cg_tensor* tokens, cg_tensor** logits_out) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !tokens) return CG_ERR_INVALID;
   cg_ctx* c = D->c;
   if (!D->finalized || D->B == 0) return fail(c, CG_ERR_INVALID, "decoder: prefill first");
@@ -1111,6 +1120,7 @@ int32_t cg_decoder_tokens(cg_decoder* D, cg_tensor** out) {
 
 int32_t cg_decoder_generate(cg_decoder* D, const uint32_t* prompt, int32_t batch, int32_t seq, int32_t n_decode,
                             uint32_t* out) {
+  CG_LAZY_EAGER_SCOPE(D ? D->c : nullptr);
   if (!D || !prompt || !out || batch < 1 || seq < 1 || n_decode < 0) return CG_ERR_INVALID;
   cg_ctx* c = D->c;
   cg_tensor* tk = nullptr;

@@ -506,6 +506,14 @@ static bool same_shape(const cg_tensor* a, const cg_tensor* b) {
 template <int OP>
 static int binary(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, cg_tensor** out) {
   if (!c || !a || !b || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (c->lazy && !c->lazy_busy) {
+    constexpr int lb = OP == OP_ADD ? LB_ADD : OP == OP_SUB ? LB_SUB : OP == OP_MUL ? LB_MUL : OP == OP_DIV ? LB_DIV
+                       : OP == OP_POW ? LB_POW : OP == OP_LT ? LB_LT : -1;
+    int st = CG_OK;
+    if (lb >= 0 && lazy_binary(c, lb, a, b, out, &st)) return st;
+    CG_LAZY_NEED(c, a);
+    CG_LAZY_NEED(c, b);
+  }
   if (a->tag != b->tag) return fail(c, CG_ERR_DTYPE, "mixed dtypes in binary operation");
   if (!same_shape(a, b)) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
   Hold r;
@@ -540,6 +548,11 @@ template <int OP>
 static int unary(cg_ctx* c, const cg_tensor* x, cg_tensor** out, const char* name) {
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (OP != UN_NEG && x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, std::string("Invalid input types for ") + name);
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (OP == UN_NEG && lazy_unary_neg(c, x, out, &st)) return st;
+    CG_LAZY_NEED(c, x);
+  }
   Hold r;
   CG_TRY(new_tensor(c, x->tag, x->tag == CG_F32 ? ST_F32 : ST_U32, x->dims, x->rank, &r.t));
   const int64_t n = r.t->numel();
@@ -559,6 +572,11 @@ static int unary(cg_ctx* c, const cg_tensor* x, cg_tensor** out, const char* nam
 template <int RED>
 static int reduce(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (RED != RED_ARGMAX && x->rank > 0 && lazy_reduce(c, RED == RED_MAX ? LR_MAX : LR_SUM, x, out, &st)) return st;
+    CG_LAZY_NEED(c, x);
+  }
   const int out_tag = RED == RED_ARGMAX ? CG_U32 : x->tag;
   const int out_st = out_tag == CG_F32 ? ST_F32 : ST_U32;
   if (x->rank == 0) {
@@ -663,6 +681,10 @@ static int from_vec(cg_ctx* c, int tag, const void* data, int64_t n, const int64
     *out = b;
     return CG_OK;
   }
+  if (n == 1) {  // a literal: its value stays known on the host
+    r.t->has_scalar = true;
+    memcpy(&r.t->scalar_bits, data, 4);
+  }
   *out = r.take();
   return CG_OK;
 }
@@ -675,6 +697,7 @@ int32_t cg_ndarray_from_vec_u32(cg_ctx* c, const uint32_t* d, int64_t n, const i
 }
 
 int32_t cg_to_bf16(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
+  CG_LAZY_NEED(c, x);
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "bf16 storage is for F32-tagged tensors");
   Hold r;
@@ -685,6 +708,7 @@ int32_t cg_to_bf16(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
 }
 
 int32_t cg_to_f32(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
+  CG_LAZY_NEED(c, x);
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "not an F32-tagged tensor");
   Hold r;
@@ -702,11 +726,42 @@ int32_t cg_cast(cg_ctx* c, const cg_tensor* x, int32_t dtype, cg_tensor** out) {
     *out = const_cast<cg_tensor*>(x);
     return CG_OK;
   }
+  if (x->has_scalar && !x->node && x->numel() == 1) {
+    // a literal whose value is known on the host (e.g. the element count an rmsnorm divides by,
+    // cast from a Nat): convert it here and upload the result, no kernel
+    uint32_t bits;
+    if (dtype == CG_F32) {
+      const float v = (float)x->scalar_bits;
+      memcpy(&bits, &v, 4);
+    } else {
+      float v;
+      memcpy(&v, &x->scalar_bits, 4);
+      bits = !(v == v) ? 0u : v <= 0.f ? 0u : v >= 4294967296.f ? 0xFFFFFFFFu : (uint32_t)v;  // Rust's `as`: saturating, NaN -> 0
+    }
+    return from_vec(c, dtype, &bits, 1, x->dims, x->rank, out);
+  }
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (lazy_cast(c, x, dtype, out, &st)) return st;
+    CG_LAZY_NEED(c, x);
+  }
   Hold src;
   CG_TRY(as_contiguous_f32(c, x, &src.t));  // also widens bf16
   Hold r;
   CG_TRY(new_tensor(c, dtype, dtype == CG_F32 ? ST_F32 : ST_U32, x->dims, x->rank, &r.t));
   CG_TRY(copy_into(c, src.t, r.t->data(), r.t->storage, r.t->strides, dtype == CG_U32 ? 4 : 5));
+  if (x->has_scalar) {
+    // the literal's value follows it through the cast (f32 -> u32 saturates, NaN -> 0, as `as` does)
+    r.t->has_scalar = true;
+    if (dtype == CG_F32) {
+      const float v = (float)x->scalar_bits;
+      memcpy(&r.t->scalar_bits, &v, 4);
+    } else {
+      float v;
+      memcpy(&v, &x->scalar_bits, 4);
+      r.t->scalar_bits = !(v == v) ? 0u : v <= 0.f ? 0u : v >= 4294967296.f ? 0xFFFFFFFFu : (uint32_t)v;
+    }
+  }
   *out = r.take();
   return CG_OK;
 }
@@ -726,6 +781,7 @@ int32_t cg_sum(cg_ctx* c, const cg_tensor* x, cg_tensor** o) { return reduce<RED
 int32_t cg_argmax(cg_ctx* c, const cg_tensor* x, cg_tensor** o) { return reduce<RED_ARGMAX>(c, x, o); }
 
 int32_t cg_topk(cg_ctx* c, const cg_tensor* x, int64_t k, cg_tensor** values, cg_tensor** indices) {
+  CG_LAZY_NEED(c, x);
   if (!c || !x || !values || !indices) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "Unsupported type for topk");
   if (x->rank == 0) return fail(c, CG_ERR_SHAPE, "topk of a rank-0 tensor");
@@ -754,6 +810,8 @@ int32_t cg_topk(cg_ctx* c, const cg_tensor* x, int64_t k, cg_tensor** values, cg
 }
 
 int32_t cg_compare(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, int32_t* equal) {
+  CG_LAZY_NEED(c, a);
+  CG_LAZY_NEED(c, b);
   if (!c || !a || !b || !equal) return fail(c, CG_ERR_INVALID, "null argument");
   if (a->tag != b->tag) return fail(c, CG_ERR_DTYPE, "mixed dtypes in compare");
   *equal = 0;
@@ -778,6 +836,12 @@ int32_t cg_compare(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, int32_t* e
 
 int32_t cg_concat(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, int32_t dim, cg_tensor** out) {
   if (!c || !a || !b || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (lazy_concat(c, a, b, dim, out, &st)) return st;
+    CG_LAZY_NEED(c, a);
+    CG_LAZY_NEED(c, b);
+  }
   if (a->tag != b->tag) return fail(c, CG_ERR_DTYPE, "Incompatible types for concatenation");
   if (a->rank != b->rank || dim < 0 || dim >= a->rank) return fail(c, CG_ERR_SHAPE, "concat: rank or axis mismatch");
   for (int i = 0; i < a->rank; ++i)
@@ -796,6 +860,8 @@ int32_t cg_concat(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, int32_t dim
 }
 
 int32_t cg_index(cg_ctx* c, const cg_tensor* x, int32_t dim, const cg_tensor* indices, cg_tensor** out) {
+  CG_LAZY_NEED(c, x);
+  CG_LAZY_NEED(c, indices);
   if (!c || !x || !indices || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (indices->tag != CG_U32) return fail(c, CG_ERR_DTYPE, "Invalid input types for indexing");
   if (dim < 0 || dim >= x->rank) return fail(c, CG_ERR_SHAPE, "index: axis out of range");
@@ -837,6 +903,10 @@ int32_t cg_index(cg_ctx* c, const cg_tensor* x, int32_t dim, const cg_tensor* in
 
 int32_t cg_arange(cg_ctx* c, int64_t end, cg_tensor** out) {
   if (!c || !out || end < 0) return fail(c, CG_ERR_INVALID, "bad argument");
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (lazy_arange(c, end, out, &st)) return st;
+  }
   int64_t n = (int64_t)ceilf((float)end);
   Hold r;
   CG_TRY(new_tensor(c, CG_U32, ST_U32, &n, 1, &r.t));
@@ -850,6 +920,7 @@ int32_t cg_arange(cg_ctx* c, int64_t end, cg_tensor** out) {
 
 static int to_vec(cg_ctx* c, int tag, const cg_tensor* x, void* dst, int64_t n) {
   if (!c || !x || (!dst && n)) return fail(c, CG_ERR_INVALID, "null argument");
+  CG_LAZY_NEED(c, x);
   if (x->tag != tag) return fail(c, CG_ERR_DTYPE, "to_vec: dtype tag differs");
   if (n != x->numel()) return fail(c, CG_ERR_SHAPE, "to_vec: element count differs");
   Hold src;
@@ -862,6 +933,12 @@ int32_t cg_to_vec_u32(cg_ctx* c, const cg_tensor* x, uint32_t* dst, int64_t n) {
 
 int32_t cg_matmul(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, cg_tensor** out) {
   if (!c || !a || !b || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (c->lazy && !c->lazy_busy) {
+    int st = CG_OK;
+    if (lazy_matmul(c, a, b, out, &st)) return st;
+    CG_LAZY_NEED(c, a);
+    CG_LAZY_NEED(c, b);
+  }
   if (a->tag != b->tag) return fail(c, CG_ERR_DTYPE, "mixed dtypes in matmul");
   const int ra = a->rank, rb = b->rank;
   if (ra < 2) return fail(c, CG_ERR_SHAPE, "batched_matmul: lhs must be at least rank 2");

@@ -825,6 +825,7 @@ using namespace cg;
 extern "C" {
 
 int32_t cg_fused_rmsnorm(cg_ctx* c, const cg_tensor* x, const cg_tensor* gamma, float eps, int32_t plus_one, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !x || !gamma || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32 || gamma->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "rmsnorm wants F32 tensors");
   if (x->rank < 1 || gamma->numel() != x->dims[x->rank - 1]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
@@ -841,6 +842,7 @@ int32_t cg_fused_rmsnorm(cg_ctx* c, const cg_tensor* x, const cg_tensor* gamma, 
 }
 
 int32_t cg_fused_softmax(cg_ctx* c, const cg_tensor* x, float softcap, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "softmax wants an F32 tensor");
   if (x->rank < 1) return fail(c, CG_ERR_SHAPE, "softmax of a rank-0 tensor");
@@ -860,6 +862,7 @@ int32_t cg_fused_softmax(cg_ctx* c, const cg_tensor* x, float softcap, cg_tensor
 }
 
 int32_t cg_fused_act_mul(cg_ctx* c, const cg_tensor* gate, const cg_tensor* up, int32_t act, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !gate || !up || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (gate->tag != CG_F32 || up->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "act_mul wants F32 tensors");
   if (gate->rank != up->rank) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
@@ -886,6 +889,7 @@ int32_t cg_fused_act_mul(cg_ctx* c, const cg_tensor* gate, const cg_tensor* up, 
 }
 
 int32_t cg_fused_rope(cg_ctx* c, const cg_tensor* x, float theta, int64_t pos0, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !x || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "rope wants an F32 tensor");
   if (x->rank != 4 || (x->dims[3] & 1) || pos0 < 0) return fail(c, CG_ERR_SHAPE, "rope wants [b, heads, s, d] with even d");
@@ -914,6 +918,7 @@ int32_t cg_fused_rope(cg_ctx* c, const cg_tensor* x, float theta, int64_t pos0, 
 }
 
 int32_t cg_linear(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !x || !w || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32 || w->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "linear wants F32 tensors");
   if (x->rank < 1 || w->rank != 2 || x->dims[x->rank - 1] != w->dims[1]) return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");

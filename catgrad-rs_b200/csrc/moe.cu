@@ -670,6 +670,7 @@ using namespace cg;
 extern "C" int32_t cg_fused_moe(cg_ctx* c, const cg_tensor* x, const cg_tensor* router, const cg_tensor* gate,
                                 const cg_tensor* up, const cg_tensor* down, int32_t top_k, int32_t norm_topk, int32_t act,
                                 cg_tensor** out, cg_tensor** ids_out) {
+  CG_LAZY_EAGER_SCOPE(c);
   if (!c || !x || !router || !gate || !up || !down || !out) return fail(c, CG_ERR_INVALID, "null argument");
   if (x->tag != CG_F32 || router->tag != CG_F32 || gate->tag != CG_F32 || up->tag != CG_F32 || down->tag != CG_F32)
     return fail(c, CG_ERR_DTYPE, "moe wants F32 tensors");

@@ -130,11 +130,16 @@ cg_tensor* new_view(const cg_tensor* x) {
   memcpy(t->strides, x->strides, sizeof(t->strides));
   t->offset = x->offset;
   t->buf = x->buf;
+  t->has_scalar = x->has_scalar;
+  t->scalar_bits = x->scalar_bits;
   return t;
 }
 
 void release(cg_tensor* t) {
-  if (t && --t->rc == 0) delete t;
+  if (t && --t->rc == 0) {
+    if (t->node) lazy_orphan(t);
+    delete t;
+  }
 }
 
 Iter make_iter(int rank, const int64_t* dims, const int64_t* s0, const int64_t* s1, const int64_t* s2) {
@@ -244,6 +249,7 @@ int32_t cg_ctx_create(int32_t device, int32_t precision, void* stream, cg_ctx** 
 int32_t cg_ctx_destroy(cg_ctx* c) {
   if (!c) return CG_ERR_INVALID;
   cudaSetDevice(c->core->device);
+  if (c->lazy) lazy_flush(c);
   cudaStreamSynchronize(c->core->stream);
   cg_comm_destroy(c);
   c->core->trim();
@@ -255,6 +261,7 @@ const char* cg_last_error(cg_ctx* c) { return c ? c->err.c_str() : ""; }
 
 int32_t cg_sync(cg_ctx* c) {
   if (!c) return CG_ERR_INVALID;
+  CG_LAZY_FLUSH(c);
   int32_t flag = 0;
   CG_CUDA(c, cudaMemcpyAsync(&flag, c->core->dev_err, 4, cudaMemcpyDeviceToHost, c->core->stream));
   CG_CUDA(c, cudaStreamSynchronize(c->core->stream));
@@ -283,6 +290,11 @@ int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
     return CG_OK;
   }
   if (!strcmp(name, "resident")) { c->opt_resident = value != 0; return CG_OK; }
+  if (!strcmp(name, "lazy")) {
+    if (!value) CG_TRY(lazy_flush(c));
+    c->lazy = value != 0;
+    return CG_OK;
+  }
   if (!strcmp(name, "resident_stages")) { c->opt_res_stages = (int)value; return CG_OK; }
   if (!strcmp(name, "resident_attn_group")) {
     if (value != 0 && value != 1 && value != 2 && value != 4) return fail(c, CG_ERR_INVALID, "resident_attn_group must be 0, 1, 2 or 4");
@@ -344,6 +356,7 @@ int32_t cg_broadcast(cg_ctx* c, const cg_tensor* x, const int64_t* dims, int32_t
   cg_tensor* t = new_view(x);
   t->rank = rank;
   for (int i = 0; i < rank; ++i) { t->dims[i] = dims[i]; t->strides[i] = dims[i] == 1 ? 0 : st[i]; }
+  if (x->node) lazy_view(c, LV_BROADCAST, t, x, dims, rank);
   *out = t;
   return CG_OK;
 }
@@ -354,6 +367,7 @@ int32_t cg_transpose(cg_ctx* c, const cg_tensor* x, int32_t d0, int32_t d1, cg_t
   cg_tensor* t = new_view(x);
   std::swap(t->dims[d0], t->dims[d1]);
   std::swap(t->strides[d0], t->strides[d1]);
+  if (x->node) { const int64_t a[2] = {d0, d1}; lazy_view(c, LV_TRANSPOSE, t, x, a, 2); }
   *out = t;
   return CG_OK;
 }
@@ -365,6 +379,7 @@ int32_t cg_slice(cg_ctx* c, const cg_tensor* x, int32_t dim, int64_t start, int6
   cg_tensor* t = new_view(x);
   t->dims[dim] = len;
   t->offset += start * x->strides[dim];
+  if (x->node) { const int64_t a[3] = {dim, start, len}; lazy_view(c, LV_SLICE, t, x, a, 3); }
   *out = t;
   return CG_OK;
 }
@@ -381,6 +396,7 @@ int32_t cg_reshape(cg_ctx* c, const cg_tensor* x, const int64_t* dims, int32_t r
   Hold src;
   const cg_tensor* base = x;
   if (!reshape_view(x, dims, rank, st)) {
+    if (x->node) return lazy_reshape_copy(c, x, dims, rank, out);  // the contents do not exist yet
     CG_TRY(as_contiguous(c, x, &src.t));
     base = src.t;
     int64_t s = 1;
@@ -389,6 +405,7 @@ int32_t cg_reshape(cg_ctx* c, const cg_tensor* x, const int64_t* dims, int32_t r
   cg_tensor* t = new_view(base);
   t->rank = rank;
   for (int i = 0; i < rank; ++i) { t->dims[i] = dims[i]; t->strides[i] = st[i]; }
+  if (base->node) lazy_view(c, LV_RESHAPE, t, base, dims, rank);
   *out = t;
   return CG_OK;
 }

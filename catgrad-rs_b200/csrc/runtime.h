@@ -75,8 +75,17 @@ struct PeerXchg {
 
 }  // namespace cg
 
+namespace cg { struct LazyNode; }
+
 struct cg_ctx {
   std::shared_ptr<cg::Core> core;
+  // deferred evaluation of the trait methods ("lazy" option; lazy.cu): calls are recorded as nodes
+  // and run, with recognised chains replaced by fused kernels, when a result is needed
+  bool lazy = false;
+  bool lazy_busy = false;                 // the recorded nodes are being executed: entry points run eagerly
+  std::vector<cg::LazyNode*> lazy_nodes;
+  int64_t lazy_fused = 0;                 // chains replaced by a fused kernel so far
+  int64_t lazy_recorded = 0;              // trait calls recorded so far
   int precision = CG_PREC_F32;
   std::string err;
   int64_t launches = 0;
@@ -110,6 +119,14 @@ struct cg_tensor {
   int64_t strides[CG_MAX_RANK] = {0};  // in elements
   int64_t offset = 0;                  // in elements
   std::shared_ptr<cg::Buffer> buf;
+  // deferred evaluation: a tensor whose contents do not exist yet points at the node that will
+  // produce them (buf is null until then); lazy_uses counts recorded nodes that read this tensor
+  cg::LazyNode* node = nullptr;
+  int lazy_uses = 0;
+  // a one-element literal keeps its value on the host (carried through views), so that chains such
+  // as x / sqrt(mean + eps) can be recognised without reading device memory
+  bool has_scalar = false;
+  uint32_t scalar_bits = 0;
 
   int64_t numel() const {
     int64_t n = 1;
@@ -233,6 +250,49 @@ inline int grid_for(int64_t n, int block, int max_blocks = 148 * 16) {
   if (g > max_blocks) g = max_blocks;
   return (int)g;
 }
+
+// ---- deferred evaluation (lazy.cu) ----------------------------------------------------
+// Runs every recorded node (fused where a chain is recognised).  No-op when nothing is pending.
+int lazy_flush(cg_ctx* c);
+// Called when the last reference to a tensor that is still pending goes away.
+void lazy_orphan(cg_tensor* t);
+// Recorders: return true when the call was recorded (then *st is its status and *out the pending
+// result); false when the caller should run eagerly.
+bool lazy_binary(cg_ctx* c, int op, const cg_tensor* a, const cg_tensor* b, cg_tensor** out, int* st);
+bool lazy_unary_neg(cg_ctx* c, const cg_tensor* x, cg_tensor** out, int* st);
+bool lazy_reduce(cg_ctx* c, int red, const cg_tensor* x, cg_tensor** out, int* st);
+bool lazy_cast(cg_ctx* c, const cg_tensor* x, int dtype, cg_tensor** out, int* st);
+bool lazy_matmul(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, cg_tensor** out, int* st);
+bool lazy_concat(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, int dim, cg_tensor** out, int* st);
+bool lazy_arange(cg_ctx* c, int64_t end, cg_tensor** out, int* st);
+// A view `t` of the pending tensor `x` was just created by metadata arithmetic: register it.
+enum LazyView : int { LV_BROADCAST = 0, LV_TRANSPOSE = 1, LV_SLICE = 2, LV_RESHAPE = 3 };
+void lazy_view(cg_ctx* c, int kind, cg_tensor* t, const cg_tensor* x, const int64_t* args, int nargs);
+// reshape that needs a copy, of a pending tensor
+int lazy_reshape_copy(cg_ctx* c, const cg_tensor* x, const int64_t* dims, int rank, cg_tensor** out);
+enum LazyBin : int { LB_ADD = 0, LB_SUB, LB_MUL, LB_DIV, LB_POW, LB_LT };
+enum LazyRed : int { LR_MAX = 0, LR_SUM };
+// Run what is pending only if this tensor is part of it.
+#define CG_LAZY_NEED(ctx, t)                                                                        \
+  do {                                                                                              \
+    if ((ctx) && (ctx)->lazy && !(ctx)->lazy_busy && (t) && (t)->node) CG_TRY(cg::lazy_flush(ctx)); \
+  } while (0)
+#define CG_LAZY_FLUSH(ctx)                                                  \
+  do {                                                                      \
+    if ((ctx) && (ctx)->lazy && !(ctx)->lazy_busy) CG_TRY(cg::lazy_flush(ctx)); \
+  } while (0)
+
+// Entry points outside the recorded trait methods (fused kernels, the decoder) first run whatever
+// is pending and then execute eagerly, including the trait methods they call themselves.
+struct LazyPause {
+  cg_ctx* c;
+  bool was;
+  explicit LazyPause(cg_ctx* ctx) : c(ctx), was(ctx ? ctx->lazy_busy : false) { if (c) c->lazy_busy = true; }
+  ~LazyPause() { if (c) c->lazy_busy = was; }
+};
+#define CG_LAZY_EAGER_SCOPE(ctx) \
+  CG_LAZY_FLUSH(ctx);            \
+  cg::LazyPause lazy_pause__(ctx)
 
 // ---- entry points implemented in other translation units, used across them ----------
 

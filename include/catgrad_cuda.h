@@ -178,6 +178,20 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *             boundaries); 0 (default) = one kernel per operation, captured into a CUDA graph.
  *             Both give the same logits within bf16 rounding; the per-operation path is the
  *             faster one at the measured shapes, so it stays the default.
+ *   "lazy"  : 1 = the trait methods are RECORDED instead of run (binary ops, neg, cast, max, sum,
+ *             matmul, concat, arange and the views): each returns a handle with shape and dtype
+ *             whose contents do not exist yet.  When contents are needed -- cg_to_vec_*,
+ *             cg_compare, a method that is not recorded (sin, cos, eq, argmax, topk, index),
+ *             cg_sync, or any entry point outside the trait -- the recorded calls run in order,
+ *             with the chains catgrad's stdlib and model graphs lower to replaced by one fused
+ *             kernel each: rmsnorm (helpers.rs:120-145), softmax (nn/mod.rs:162-171),
+ *             silu(g) * u (nn/mod.rs:146-148), rope (helpers.rs:202-221) and the attention core
+ *             (models/llama.rs:97-108) seen through repeat_kv and the causal mask, so that the
+ *             S x S scores never exist.  A value inside a chain is skipped only when nothing else
+ *             reads it and the caller holds no handle to it.  Results equal eager mode's within
+ *             f32 rounding (integer and index results exactly); errors a recorded call would
+ *             raise for its shapes or dtypes are raised when it is recorded.  0 (default) = eager.
+ *             Setting it to 0 first runs what is pending.
  *   "resident_attn_group" : CTAs that share one (row, kv head) in the resident kernel's attention
  *             phase: 1, 2 or 4; 0 (default) = chosen from the batch and the cache length
  *   "wait_limit_us" : limit of every bounded device-side wait (default 1 000 000).  When a wait
@@ -186,6 +200,10 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  * A decoder re-captures its decode-step graph after any option change.
  */
 int32_t cg_set_option(cg_ctx*, const char* name, int64_t value);
+
+/* Counters of the deferred-evaluation mode: trait calls recorded so far, chains replaced by a
+ * fused kernel so far, calls currently pending.  No counterpart in the reference. */
+int32_t cg_lazy_stats(cg_ctx*, int64_t* recorded, int64_t* fused, int64_t* pending);
 
 /* Failure-path probe: enqueues one small kernel that waits (bounded by "wait_limit_us") on a
  * flag of the context that nothing ever raises.  The wait runs out, the kernel returns, and the
