@@ -61,6 +61,10 @@ extern "C" {
     fn cg_decoder_set_param(d: *mut cg_decoder, name: *const c_char, t: *const ffi::cg_tensor) -> i32;
     fn cg_decoder_finalize(d: *mut cg_decoder) -> i32;
     fn cg_decoder_generate(d: *mut cg_decoder, prompt: *const u32, batch: i32, seq: i32, n_decode: i32, out: *mut u32) -> i32;
+    fn cg_decoder_load_safetensors(d: *mut cg_decoder, path: *const c_char) -> i32;
+    fn cg_decoder_append(d: *mut cg_decoder, tokens: *const ffi::cg_tensor, logits_out: *mut *mut ffi::cg_tensor) -> i32;
+    fn cg_decoder_truncate(d: *mut cg_decoder, positions: i64) -> i32;
+    fn cg_decoder_tokens(d: *mut cg_decoder, out: *mut *mut ffi::cg_tensor) -> i32;
 }
 
 pub struct Decoder {
@@ -95,6 +99,70 @@ impl Decoder {
             cg_decoder_generate(self.raw, prompt.as_ptr(), batch as i32, seq as i32, n_decode as i32, out.as_mut_ptr())
         });
         out
+    }
+}
+
+impl Decoder {
+    /// Hand over every tensor of a .safetensors file (call once per shard, then `finalize`): replaces
+    /// the host-side loading of catgrad-llm/examples/llama/main.rs:279-354.
+    pub fn load_safetensors(&mut self, path: &str) {
+        let c = CString::new(path).expect("path");
+        self.backend.check(unsafe { cg_decoder_load_safetensors(self.raw, c.as_ptr()) });
+    }
+
+    /// Run `tokens` (one row) on top of the cached positions and return the greedy next token.
+    fn append_row(&mut self, tokens: &[u32]) -> u32 {
+        use catgrad::category::core::Shape;
+        use catgrad::interpreter::backend::Backend;
+        let t = match self.backend.ndarray_from_vec_u32(tokens.to_vec(), Shape(vec![1, tokens.len()])) {
+            Ok(catgrad::interpreter::TaggedTensor::U32([t])) => t,
+            _ => panic!("token upload failed"),
+        };
+        self.backend.check(unsafe { cg_decoder_append(self.raw, t.raw(), std::ptr::null_mut()) });
+        let mut hist = std::ptr::null_mut();
+        self.backend.check(unsafe { cg_decoder_tokens(self.raw, &mut hist) });
+        let hist = crate::CudaTensor::from_raw(hist);
+        match self.backend.to_vec(catgrad::interpreter::TaggedTensor::U32([hist])) {
+            catgrad::interpreter::TaggedVec::U32(v) => *v.last().expect("one generated token"),
+            _ => unreachable!(),
+        }
+    }
+}
+
+/// `serve::LM` (catgrad-llm/src/serve.rs:12-20) over the fused decoder, the way the reference's
+/// `ModelRunner` implements it (catgrad-llm/src/run.rs:262-305), except that `set_context` keeps the
+/// longest common prefix of the old and the new context in the cache instead of all or nothing.
+pub struct DecoderLM {
+    dec: Decoder,
+    eos: Vec<u32>,
+    cached: Vec<u32>,
+    pending: Vec<u32>,
+}
+
+impl DecoderLM {
+    pub fn new(dec: Decoder, eos: Vec<u32>) -> Self { DecoderLM { dec, eos, cached: vec![], pending: vec![] } }
+
+    pub fn set_context(&mut self, context: Vec<u32>) {
+        let mut n = self.cached.iter().zip(context.iter()).take_while(|(a, b)| a == b).count();
+        if n == context.len() && n > 0 { n -= 1; }  // at least one token must run to get a next token
+        if n < self.cached.len() {
+            self.dec.backend.check(unsafe { cg_decoder_truncate(self.dec.raw, n as i64) });
+            self.cached.truncate(n);
+        }
+        self.pending = context[n..].to_vec();
+    }
+}
+
+impl Iterator for DecoderLM {
+    type Item = u32;
+    fn next(&mut self) -> Option<u32> {
+        let tokens = std::mem::take(&mut self.pending);
+        if tokens.is_empty() { return None; }
+        let token = self.dec.append_row(&tokens);
+        self.cached.extend(tokens);
+        if self.eos.contains(&token) { return None; }  // EOS tokens are not emitted (run.rs:252-255)
+        self.pending.push(token);
+        Some(token)
     }
 }
 

@@ -50,4 +50,8 @@ extern "C" {
     pub fn cg_arange(ctx: C, end: i64, out: *mut T) -> i32;
     pub fn cg_to_vec_f32(ctx: C, x: *const cg_tensor, dst: *mut f32, n: i64) -> i32;
     pub fn cg_to_vec_u32(ctx: C, x: *const cg_tensor, dst: *mut u32, n: i64) -> i32;
+    // extensions the shim exposes
+    pub fn cg_sync(ctx: C) -> i32;
+    pub fn cg_set_option(ctx: C, name: *const c_char, value: i64) -> i32;
+    pub fn cg_lazy_stats(ctx: C, recorded: *mut i64, fused: *mut i64, pending: *mut i64) -> i32;
 }

@@ -43,6 +43,8 @@ impl Clone for CudaTensor {
 }
 impl CudaTensor {
     pub(crate) fn raw(&self) -> *const ffi::cg_tensor { self.0 }
+    /// Takes over one reference returned by the library.
+    pub(crate) fn from_raw(p: *mut ffi::cg_tensor) -> Self { CudaTensor(p) }
 }
 impl Drop for CudaTensor { fn drop(&mut self) { unsafe { ffi::cg_tensor_release(self.0); } } }
 impl std::fmt::Debug for CudaTensor {
@@ -66,6 +68,22 @@ impl CudaBackend {
         assert_eq!(st, 0, "cg_ctx_create failed: no CUDA device? (there is no CPU fallback)");
         CudaBackend { ctx: Arc::new(Ctx(ctx)) }
     }
+    /// Record the trait calls instead of running them and fuse the stdlib's chains (rmsnorm, softmax,
+    /// silu * up, rope, the attention core) when a result is needed.  The interpreter and the model
+    /// graphs above stay exactly as they are.
+    pub fn lazy(self, on: bool) -> Self {
+        let name = std::ffi::CString::new("lazy").unwrap();
+        self.check(unsafe { ffi::cg_set_option(self.ctx.0, name.as_ptr(), on as i64) });
+        self
+    }
+    /// (trait calls recorded, chains fused, calls pending)
+    pub fn lazy_stats(&self) -> (i64, i64, i64) {
+        let (mut a, mut b, mut c) = (0i64, 0i64, 0i64);
+        self.check(unsafe { ffi::cg_lazy_stats(self.ctx.0, &mut a, &mut b, &mut c) });
+        (a, b, c)
+    }
+    /// Run everything pending and surface device-side errors.
+    pub fn sync(&self) { self.check(unsafe { ffi::cg_sync(self.ctx.0) }); }
     pub(crate) fn raw_ctx(&self) -> *mut ffi::cg_ctx { self.ctx.0 }
     pub(crate) fn check(&self, st: i32) {
         if st != 0 {
