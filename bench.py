@@ -215,7 +215,7 @@ def torch_cpu_kv_baseline(cg, cfg, prompt_len: int, decode_steps: int, batch: in
                       f"({t_step * 1e3:.0f} ms each); job = {batch} rows x (prefill + {decode_steps} steps), estimated from those"}
 
 
-def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local):
+def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local, host_weights=True):
     """Compare the token history [B, 1 + T] the timed job produced with an independent run that
     is teacher-forced with those tokens (so one flipped near-tie does not cascade): at one GPU
     the same decoder stepping one kernel per operation, eagerly, one step at a time; under tensor
@@ -228,7 +228,10 @@ def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local):
         other, vs = dec, "the same decoder run eagerly, one kernel per operation, one step per call"
     else:
         other = cg.Decoder(C, cfg, max_seq=prompt.shape[1] + T + 1, max_batch=B, tp_rank=0, tp_world=1)
-        other.load(cg.synth.make_weights(cfg, 0))
+        if host_weights:
+            other.load(cg.synth.make_weights(cfg, 0))
+        else:
+            other.load_random(cfg, 0)   # the same device-drawn checkpoint the job used
         vs = "a one-GPU (tp_world = 1) decoder built by rank 0 on its own GPU"
     try:
         other.reset()
@@ -298,6 +301,12 @@ def main():
     ap.add_argument("--prompt", type=int, default=0)
     ap.add_argument("--decode", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp", "ep"],
+                    help="with several GPUs: tp (default) = the model is tensor-parallel over the ranks, the configuration the "
+                         "metric names; dp = every rank holds the whole model and runs its share of the batch rows, no "
+                         "collective on the data path (what pays for a model this small: see DESIGN.md); ep (mixture-of-experts "
+                         "workloads) = data-parallel attention with the experts split over the ranks, rows all-gathered and expert "
+                         "sums reduce-scattered on every expert layer")
     ap.add_argument("--path", default="decoder", choices=["decoder", "trait"],
                     help="decoder (default): the fused KV-cached runner, the line the metric is quoted on; trait: the "
                          "reference's unchanged op stream through the 28 trait methods, prefill only, eager and recorded")
@@ -362,7 +371,13 @@ def main():
     for kv in args.opt:
         name, _, val = kv.partition("=")
         C.set_option(name, int(val))
-    if world > 1:
+    ep = world > 1 and args.parallelism == "ep"
+    dp = world > 1 and args.parallelism in ("dp", "ep")   # rows are split over the ranks in both
+    if dp and B % world:
+        raise SystemExit(f"--parallelism dp needs the batch ({B}) to divide by the ranks ({world})")
+    tpw, tpr = (1, 0) if dp else (world, rank)   # tensor-parallel degree and place of this rank's decoder
+    Bl = B // world if dp else B                 # rows this rank runs
+    if world > 1 and (ep or not dp):
         importlib.import_module("catgrad-rs_b200.tp").init_comm(C, rank, world)
         mapped, why = C.peer_exchange()
         collective = "decode: partial products pushed over mapped peer memory, no collective call; prefill: NCCL" if mapped \
@@ -371,7 +386,8 @@ def main():
     if args.path == "trait":
         return trait_path(cg, C, cfg, args, B, S, workload)
 
-    dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=B, tp_rank=rank, tp_world=world)
+    dec = cg.Decoder(C, cfg, max_seq=S + T + 1, max_batch=Bl, tp_rank=tpr, tp_world=tpw,
+                     ep_rank=rank if ep else 0, ep_world=world if ep else 1)
     if headline:
         dec.load(synth.make_weights(cfg, 0))
         generator = f"numpy {np.__version__} PCG64, weights seed 0 N(0,0.02) rounded to bf16, ids seed 1"
@@ -379,6 +395,8 @@ def main():
         dec.load_random(cfg, 0)  # tens of GB: drawn on the device instead of crossing the host link
         generator = "weights N(0,0.02) from the library's counter-based device generator (seed 0), ids numpy PCG64 seed 1"
     prompt = synth.make_tokens(cfg, B, S, seed=1)
+    if dp:
+        prompt = np.ascontiguousarray(prompt[rank * Bl:(rank + 1) * Bl])   # this rank's rows of the job
     prompt_dev = C.from_numpy(prompt)
     C.sync()
 
@@ -426,7 +444,7 @@ def main():
     clocks = sampler.stop()
 
     # what was timed is checked: the job's greedy tokens against an independent run
-    token_check = check_tokens(cg, C, dec, cfg, prompt, out_tokens, T, rank, world, local)
+    token_check = check_tokens(cg, C, dec, cfg, prompt, out_tokens, T, rank, world if ep else tpw, local, headline)
     if dist is not None:
         dist.barrier()
 
@@ -435,17 +453,17 @@ def main():
     dec.prefill(prompt_dev)
     dec.decode(1)
     ms_decode = timed(lambda: dec.decode(T - 1), 1) / max(T - 1, 1)
-    gemm_ms, gemm_launches = dec.time_gemms(B, 20)
+    gemm_ms, gemm_launches = dec.time_gemms(Bl, 20)
     peak, peak_kind = measured_peaks()
-    weight_bytes = 2 * dense_params_per_step(cfg) / world
-    kv_bytes = B * synth.kv_bytes_per_token(cfg) * (S + T / 2) / world
+    weight_bytes = 2 * dense_params_per_step(cfg) / tpw
+    kv_bytes = Bl * synth.kv_bytes_per_token(cfg) * (S + T / 2) / tpw
     expert_bytes = 0.0
     if cfg.num_local_experts > 1:
         # expected distinct experts a step of B tokens touches under uniform routing, per sparse layer
         E, k = cfg.num_local_experts, cfg.num_experts_per_tok
-        distinct = E * (1.0 - (1.0 - 1.0 / E) ** (B * k))
+        distinct = E * (1.0 - (1.0 - 1.0 / E) ** (Bl * k))
         sparse_layers = sum(1 for i in range(cfg.num_hidden_layers) if (i + 1) % cfg.decoder_sparse_step == 0)
-        expert_bytes = sparse_layers * distinct * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2 / world
+        expert_bytes = sparse_layers * distinct * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2 / tpw
     achieved = weight_bytes / (gemm_ms * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -458,13 +476,15 @@ def main():
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": f"tp{world}",
-                   **({"tp_collective": collective} if world > 1 else {}),
+        "config": {"workload": workload, "global_batch": B, "prompt": S, "decode": T, "parallelism": (f"ep{world}: dense weights whole and 1/{world} of the experts per GPU, {Bl} rows each, all-gather + "
+                                   "reduce-scatter per expert layer" if ep else
+                                   f"dp{world}: whole model per GPU, {Bl} rows each, no collective" if dp else f"tp{world}"),
+                   **({"tp_collective": collective} if world > 1 and not dp else {}),
                    "l2": "inputs larger than L2: every decode step streams the full weight set "
                          f"({weight_bytes / 1e9:.2f} GB per GPU) plus the KV cache",
                    "generator": generator},
         "clocks": clocks,
-        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(prompt.nbytes),
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": int(prompt.nbytes) * (world if dp else 1),
                 "d2h_bytes_per_step": int(B * (T + 1) * 4)},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "k_gemm_dec (k_gemm_tc for the LM head): all dense weight-streaming GEMMs of one decode step",

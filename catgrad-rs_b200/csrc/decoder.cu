@@ -81,6 +81,8 @@ struct cg_decoder {
   cg_tensor *m_ids = nullptr, *m_wts = nullptr, *m_pos = nullptr, *m_tiles = nullptr, *m_xg = nullptr, *m_h = nullptr,
             *m_y = nullptr, *m_xs3 = nullptr, *m_logits = nullptr;
   int El = 0;                    // experts on this rank
+  int EW = 1, ER = 0;            // ranks the experts are split over, and this rank's place among them
+  cg_tensor *ep_x = nullptr, *ep_y = nullptr;  // expert parallelism: every rank's rows gathered / this rank's expert sums for them
   bool pending_reduce = false;   // x still lacks the addends pushed by the last row-parallel GEMM
   // norm hand-over (see DecGemm): xn holds bf16(x * gain) un-normalised and ss the per-CTA sums
   // of squares the last residual GEMM wrote; the next GEMM applies 1 / rms in its epilogue
@@ -152,7 +154,9 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   int64_t s2[2];
   s2[0] = M; s2[1] = H;
   CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->x));
+  s2[0] = M * (D->cfg.ep_world > 1 ? D->cfg.ep_world : 1);  // the expert block normalises every rank's rows
   CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->xn));
+  s2[0] = M;
   CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->tmp));
   s2[1] = D->qkv;
   CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->qkvb));
@@ -164,6 +168,15 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
   if (D->cfg.n_experts > 0) {
     drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
     drop(D->m_xs3); drop(D->m_logits);
+    const int64_t M_local = M;
+    const int epw = D->cfg.ep_world > 1 ? D->cfg.ep_world : 1;
+    M = M * epw;  // under expert parallelism the expert block sees the rows of every rank
+    drop(D->ep_x); drop(D->ep_y);
+    if (epw > 1) {
+      s2[0] = M; s2[1] = H;
+      CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->ep_x));
+      CG_TRY(new_tensor(c, CG_F32, ST_F32, s2, 2, &D->ep_y));
+    }
     s2[0] = M; s2[1] = 3 * H;
     CG_TRY(new_tensor(c, CG_F32, ST_BF16, s2, 2, &D->m_xs3));
     s2[1] = D->cfg.n_experts;
@@ -183,9 +196,22 @@ int ensure_workspace(cg_decoder* D, int64_t M) {
     // rows of a tile past its group are computed and discarded: keep them finite
     CG_CUDA(c, cudaMemsetAsync(D->m_xg->data(), 0, (size_t)P * H * 2, c->core->stream));
     CG_CUDA(c, cudaMemsetAsync(D->m_h->data(), 0, (size_t)P * D->cfg.moe_ffn * 2, c->core->stream));
+    M = M_local;
   }
   D->cap = M;
   return CG_OK;
+}
+
+// x += t
+__global__ void k_add_rows(float* x, const float* t, int64_t n) {
+  const int64_t n4 = n / 4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 a = ((float4*)x)[i];
+    const float4 b = ((const float4*)t)[i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    ((float4*)x)[i] = a;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) x[n4 * 4 + threadIdx.x] += t[n4 * 4 + threadIdx.x];
 }
 
 // The expert block of layer L on M tokens; under tensor parallelism every rank owns whole
@@ -207,12 +233,12 @@ int moe_block(cg_decoder* D, Layer& L, int64_t M, bool push = false) {
   a.w_up = (const __nv_bfloat16*)L.we_up->data();
   a.w_down = (const __nv_bfloat16*)L.we_down->data();
   a.H = (int)D->H; a.E = cfg.n_experts; a.k = cfg.top_k; a.Fe = cfg.moe_ffn; a.norm_topk = cfg.norm_topk; a.act = cfg.act;
-  a.e_lo = cfg.tp_rank * D->El; a.El = D->El;
+  a.e_lo = D->ER * D->El; a.El = D->El;
   a.add_residual = cfg.tp_world > 1 && cfg.tp_rank != 0 ? 0 : 1;
   a.M = M;
   a.xn = (__nv_bfloat16*)D->xn->data();
   int32_t* t = (int32_t*)D->m_tiles->data();
-  const int64_t Pc = D->cap * cfg.top_k;
+  const int64_t Pc = D->cap * (cfg.ep_world > 1 ? cfg.ep_world : 1) * cfg.top_k;
   a.w.ids = (uint32_t*)D->m_ids->data();
   a.w.wts = (float*)D->m_wts->data();
   a.w.pos = (int32_t*)D->m_pos->data();
@@ -221,6 +247,27 @@ int moe_block(cg_decoder* D, Layer& L, int64_t M, bool push = false) {
   a.w.h = (__nv_bfloat16*)D->m_h->data();
   a.w.y = (float*)D->m_y->data();
   (void)P;
+  if (cfg.ep_world > 1) {
+    // Expert parallelism with data-parallel attention: gather every rank's rows, route them (the
+    // same f32 arithmetic on the same numbers on every rank, so the expert ids agree everywhere),
+    // run the experts this rank owns on all of them, and hand every rank the sum over all experts
+    // for its own rows.
+    cg_ctx* c = D->c;
+    if (!c->comm) return fail(c, CG_ERR_COMM, "decoder: expert parallelism needs cg_comm_init first");
+    const int64_t n = M * D->H;
+    ncclResult_t r = nccl().AllGather(D->x->data(), D->ep_x->data(), (size_t)n, ncclFloat32, (ncclComm_t)c->comm, c->core->stream);
+    if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllGather: ") + nccl().GetErrorString(r));
+    a.x = (const float*)D->ep_x->data();
+    a.out = (float*)D->ep_y->data();
+    a.M = M * cfg.ep_world;
+    a.add_residual = 0;
+    CG_TRY(moe_ffn(c, a));
+    r = nccl().ReduceScatter(D->ep_y->data(), D->tmp->data(), (size_t)n, ncclFloat32, ncclSum, (ncclComm_t)c->comm, c->core->stream);
+    if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclReduceScatter: ") + nccl().GetErrorString(r));
+    k_add_rows<<<grid_for((n + 3) / 4, 256), 256, 0, c->core->stream>>>((float*)D->x->data(), (const float*)D->tmp->data(), n);
+    CG_LAUNCHED(c);
+    return CG_OK;
+  }
   PeerPush px;
   if (push) {
     // decode under tensor parallelism: no collective call (see project_add)
@@ -642,6 +689,9 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
     if (k.post_norms) return fail(c, CG_ERR_UNSUPPORTED, "decoder: expert layers with post-norms are not supported");
   }
   if (k.tp_rank < 0 || k.tp_rank >= W) return fail(c, CG_ERR_INVALID, "decoder: tp_rank out of range");
+  const int EPW = k.ep_world < 1 ? 1 : k.ep_world;
+  if (EPW > 1 && (W != 1 || k.n_experts <= 0 || k.n_experts % EPW || k.ep_rank < 0 || k.ep_rank >= EPW))
+    return fail(c, CG_ERR_INVALID, "decoder: expert parallelism needs tp_world = 1, experts divisible by ep_world and ep_rank in range");
   // fewer kv heads than ranks: every kv head is replicated on W / n_kv_heads consecutive ranks
   const bool kv_ok = k.n_kv_heads % W == 0 || (k.n_kv_heads < W && W % k.n_kv_heads == 0);
   if (k.n_heads % k.n_kv_heads || k.n_heads % W || !kv_ok || k.ffn % W || k.vocab % W)
@@ -660,7 +710,9 @@ int32_t cg_decoder_create(cg_ctx* c, const cg_decoder_config* cfg, cg_decoder** 
   D->F = k.ffn / W;
   D->Vp = k.vocab / W;
   D->qkv = (D->nh + 2 * D->nkv) * D->d;
-  D->El = k.n_experts > 0 ? k.n_experts / W : 0;
+  D->EW = EPW > 1 ? EPW : W;
+  D->ER = EPW > 1 ? k.ep_rank : k.tp_rank;
+  D->El = k.n_experts > 0 ? k.n_experts / D->EW : 0;
   *out = D;
   return CG_OK;
 }
@@ -682,7 +734,7 @@ int32_t cg_decoder_destroy(cg_decoder* D) {
   drop(D->logits); drop(D->x); drop(D->xn); drop(D->qkvb); drop(D->q); drop(D->att); drop(D->hact);
   drop(D->tmp); drop(D->xl); drop(D->splitk); drop(D->best); drop(D->ss);
   drop(D->m_ids); drop(D->m_wts); drop(D->m_pos); drop(D->m_tiles); drop(D->m_xg); drop(D->m_h); drop(D->m_y);
-  drop(D->m_xs3); drop(D->m_logits);
+  drop(D->m_xs3); drop(D->m_logits); drop(D->ep_x); drop(D->ep_y);
   delete D;
   return CG_OK;
 }
@@ -788,7 +840,7 @@ int32_t cg_decoder_finalize(cg_decoder* D) {
       }
       for (auto pr : {std::make_pair(eg, &L.we_gate), std::make_pair(eu, &L.we_up), std::make_pair(ed, &L.we_down)}) {
         cg_tensor* sl = nullptr;
-        CG_TRY(cg_slice(c, pr.first, 0, (int64_t)R * El, El, &sl));
+        CG_TRY(cg_slice(c, pr.first, 0, (int64_t)D->ER * El, El, &sl));
         Hold hs(sl);
         if (sl->storage == ST_BF16 && sl->contiguous()) { sl->rc++; *pr.second = sl; }  // already in the layout the GEMM reads
         else CG_TRY(cg_to_bf16(c, sl, pr.second));

@@ -28,13 +28,13 @@ class DecoderConfig(C.Structure):
         ("rope_original_max_pos", C.c_int32),
         ("rope_local_theta", C.c_float), ("rope_local_every", C.c_int32),
         ("n_experts", C.c_int32), ("top_k", C.c_int32), ("moe_ffn", C.c_int32), ("norm_topk", C.c_int32),
-        ("tp_rank", C.c_int32), ("tp_world", C.c_int32),
+        ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("ep_rank", C.c_int32), ("ep_world", C.c_int32),
     ]
 
 
 class Decoder:
     def __init__(self, backend: CudaBackend, cfg, max_seq: int, max_batch: int, tp_rank: int = 0, tp_world: int = 1,
-                 **switches):
+                 ep_rank: int = 0, ep_world: int = 1, **switches):
         self.B = backend
         L = backend._lib
         vp, i32 = _c_vp, C.c_int32
@@ -75,6 +75,8 @@ class Decoder:
         c.max_batch = max_batch
         c.tp_rank = tp_rank
         c.tp_world = tp_world
+        c.ep_rank = ep_rank
+        c.ep_world = ep_world
         rs = getattr(cfg, "rope_scaling", None)
         if rs:
             # {"rope_type": "llama3" | "yarn", "factor": ..., ...} as in a checkpoint's config.json

@@ -50,6 +50,8 @@ pub struct DecoderConfig {
     pub norm_topk: i32,
     pub tp_rank: i32,
     pub tp_world: i32,
+    pub ep_rank: i32,
+    pub ep_world: i32,
 }
 
 #[repr(C)]

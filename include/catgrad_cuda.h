@@ -314,6 +314,15 @@ typedef struct cg_decoder_config {
    * replicated), whole experts are owned by ranks. */
   int32_t tp_rank;
   int32_t tp_world;
+  /* expert parallelism with data-parallel attention (qwen3.rs:64-133 sharded over ranks; needs
+   * tp_world = 1 and cg_comm_init): every rank holds the dense weights whole and n_experts /
+   * ep_world experts, runs ITS OWN batch rows (the caller hands each rank its rows), and on every
+   * expert layer the rows of all ranks are all-gathered, routed identically everywhere (f32),
+   * run through the experts this rank owns, and the expert sums reduce-scattered back to the
+   * rows' owners.  With top-8 of 128 experts on 8 ranks a token visits nearly every rank, so
+   * this moves the bytes an all-to-all dispatch / combine would.  0 or 1 = off. */
+  int32_t ep_rank;
+  int32_t ep_world;
 } cg_decoder_config;
 
 int32_t cg_decoder_create(cg_ctx*, const cg_decoder_config* cfg, cg_decoder** out);

@@ -193,3 +193,73 @@ def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, peer, cfg_expr):
     same = (got[n:n + toks.size].reshape(toks.shape).astype(np.uint32) == toks).mean()
     assert same >= 0.8, same  # summation order differs across ranks; near-ties may flip a token
     np.testing.assert_allclose(got[n + toks.size:], step_lg, rtol=0, atol=2e-2)
+
+
+EP_WORKER = textwrap.dedent("""
+    import importlib, os, sys
+    import numpy as np
+    import torch, torch.distributed as dist
+    sys.path.insert(0, {root!r})
+    cg = importlib.import_module("catgrad-rs_b200")
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    C = cg.CudaBackend(local, cg.PREC_BF16)
+    cg.tp.init_comm(C, rank, world)
+    cfg = {cfg_expr}
+    rows = 2
+    prompt = cg.synth.make_tokens(cfg, rows * world, 40, seed=2)[rank * rows:(rank + 1) * rows]   # this rank's rows
+    dec = cg.Decoder(C, cfg, max_seq=64, max_batch=rows, ep_rank=rank, ep_world=world)
+    dec.load(cg.synth.make_weights(cfg, 0))
+    lg = C.to_numpy(dec.prefill(C.from_numpy(prompt), want_logits=True))
+    toks = dec.generate(np.ascontiguousarray(prompt), 10)
+    dec.prefill(C.from_numpy(prompt))
+    forced = np.uint32([[7, 8], [100, 200], [5, 5]])
+    step_lg = [C.to_numpy(dec.step_with(C.from_numpy(forced[i]), want_logits=True)) for i in range(3)]
+    np.save({out!r} + str(rank) + ".npy", np.concatenate([lg.ravel(), toks.ravel().astype(np.float32)] + [a.ravel() for a in step_lg]))
+    dec.close()
+    dist.barrier()
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.gpu
+def test_expert_parallel_decoder_matches_one_gpu(tmp_path):
+    """Expert parallelism with data-parallel attention (`ep_world`): every rank runs its own batch rows
+    and half of the experts; the rows of all ranks are gathered before each expert layer, routed
+    identically on every rank, and the expert sums reduce-scattered back.  Every rank's rows must
+    reproduce a one-GPU run of the same rows: f32 sums differ only in the order the two ranks'
+    expert contributions are added, so logits agree to 2e-3 and the greedy tokens follow."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "ep_rank")
+    script = tmp_path / "ep_gpu_worker.py"
+    script.write_text(EP_WORKER.format(root=ROOT, out=out, cfg_expr=MOE_CFG))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29613", str(script)],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    C = cg.CudaBackend(0, cg.PREC_BF16)
+    cfg = eval(MOE_CFG)
+    full = cg.synth.make_tokens(cfg, 4, 40, seed=2)
+    dec = cg.Decoder(C, cfg, max_seq=64, max_batch=2)
+    dec.load(cg.synth.make_weights(cfg, 0))
+    forced = np.uint32([[7, 8], [100, 200], [5, 5]])
+    for rank in range(2):
+        got = np.load(out + str(rank) + ".npy")
+        prompt = np.ascontiguousarray(full[rank * 2:(rank + 1) * 2])
+        dec.reset()
+        lg = C.to_numpy(dec.prefill(C.from_numpy(prompt), want_logits=True))
+        dec.reset()
+        toks = dec.generate(prompt, 10)
+        dec.reset()
+        dec.prefill(C.from_numpy(prompt))
+        step_lg = np.concatenate([C.to_numpy(dec.step_with(C.from_numpy(forced[i]), want_logits=True)).ravel() for i in range(3)])
+        n = lg.size
+        np.testing.assert_allclose(got[:n].reshape(lg.shape), lg, rtol=0, atol=2e-3)
+        same = (got[n:n + toks.size].reshape(toks.shape).astype(np.uint32) == toks).mean()
+        assert same >= 0.9, same
+        np.testing.assert_allclose(got[n + toks.size:], step_lg, rtol=0, atol=2e-3)
+    dec.close()
