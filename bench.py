@@ -9,10 +9,12 @@ strided copy at the end).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-N > 1 is launched by torchrun, one rank per GPU; the model is tensor-parallel over the N
-ranks.  Decode steps exchange the partial products of the two row-split projections of every
-layer through mapped peer memory (plain stores and flags, no collective call); prefill uses an
-NCCL all-reduce with a bf16 payload.
+N > 1 is launched by torchrun, one rank per GPU.  `--parallelism` says how the fixed job is spread:
+tp = the model is tensor-parallel over the N ranks (decode steps exchange the partial products of
+the two row-split projections of every layer through mapped peer memory, plain stores and flags,
+no collective call; prefill uses an NCCL all-reduce with a bf16 payload); dp = whole model per
+GPU, batch rows split, no collective; ep = experts and rows split, all-gather + reduce-scatter on
+every expert layer.  The default picks by model size (choose_parallelism).
 
 `--impl reference` times the CPU restatement of the reference's ndarray backend running the
 reference's own op stream (one full forward per generated token, no KV cache) on the host
@@ -215,6 +217,24 @@ def torch_cpu_kv_baseline(cg, cfg, prompt_len: int, decode_steps: int, batch: in
                       f"({t_step * 1e3:.0f} ms each); job = {batch} rows x (prefill + {decode_steps} steps), estimated from those"}
 
 
+def choose_parallelism(asked: str, cfg, batch: int, world: int) -> str:
+    """How a fixed job is spread over `world` GPUs.  A decode step costs (weight bytes this GPU
+    streams) / (HBM bandwidth) plus a per-layer chain of small dependent kernels that sharding does
+    not shorten and that tensor parallelism lengthens by two cross-GPU hand-overs per layer.  Where
+    the first term dominates (dense weights of 8 GB and more per step: the 8B shape) the model is
+    split (tp).  Where it does not (the 1B shape: 2.5 GB, 0.38 ms of a 0.9 ms step) every GPU keeps
+    the whole model and takes its share of the batch rows (dp): nothing crosses NVLink on the data
+    path, prefill divides by the number of GPUs and decode steps run on fewer rows.  Mixture-of-
+    experts models split the experts and the rows (ep).  Measured on the 1B shape at 2 GPUs: dp
+    45.6 k tok/s, tp 31.2 k, one GPU 41.7 k."""
+    if world == 1 or asked != "auto":
+        return asked if asked != "auto" else "tp"
+    rows_split = batch % world == 0
+    if cfg.num_local_experts > 1:
+        return "ep" if rows_split and cfg.num_local_experts % world == 0 else "tp"
+    return "tp" if 2 * dense_params_per_step(cfg) >= 8e9 or not rows_split else "dp"
+
+
 def check_tokens(cg, C, dec, cfg, prompt, job_tokens, T, rank, world, local, host_weights=True):
     """Compare the token history [B, 1 + T] the timed job produced with an independent run that
     is teacher-forced with those tokens (so one flipped near-tie does not cascade): at one GPU
@@ -301,12 +321,12 @@ def main():
     ap.add_argument("--prompt", type=int, default=0)
     ap.add_argument("--decode", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp", "ep"],
-                    help="with several GPUs: tp (default) = the model is tensor-parallel over the ranks, the configuration the "
-                         "metric names; dp = every rank holds the whole model and runs its share of the batch rows, no "
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp", "ep"],
+                    help="with several GPUs: tp = the model is tensor-parallel over the ranks; dp = every rank holds the whole model and runs its share of the batch rows, no "
                          "collective on the data path (what pays for a model this small: see DESIGN.md); ep (mixture-of-experts "
                          "workloads) = data-parallel attention with the experts split over the ranks, rows all-gathered and expert "
-                         "sums reduce-scattered on every expert layer")
+                         "sums reduce-scattered on every expert layer; auto (default) = the fastest of these for the model and batch by "
+                         "the rule in choose_parallelism(): tp where the weight stream dominates a decode step, rows split otherwise")
     ap.add_argument("--path", default="decoder", choices=["decoder", "trait"],
                     help="decoder (default): the fused KV-cached runner, the line the metric is quoted on; trait: the "
                          "reference's unchanged op stream through the 28 trait methods, prefill only, eager and recorded")
@@ -371,8 +391,9 @@ def main():
     for kv in args.opt:
         name, _, val = kv.partition("=")
         C.set_option(name, int(val))
-    ep = world > 1 and args.parallelism == "ep"
-    dp = world > 1 and args.parallelism in ("dp", "ep")   # rows are split over the ranks in both
+    par = choose_parallelism(args.parallelism, cfg, B, world)
+    ep = world > 1 and par == "ep"
+    dp = world > 1 and par in ("dp", "ep")   # rows are split over the ranks in both
     if dp and B % world:
         raise SystemExit(f"--parallelism dp needs the batch ({B}) to divide by the ranks ({world})")
     tpw, tpr = (1, 0) if dp else (world, rank)   # tensor-parallel degree and place of this rank's decoder
@@ -463,7 +484,7 @@ def main():
         E, k = cfg.num_local_experts, cfg.num_experts_per_tok
         distinct = E * (1.0 - (1.0 - 1.0 / E) ** (Bl * k))
         sparse_layers = sum(1 for i in range(cfg.num_hidden_layers) if (i + 1) % cfg.decoder_sparse_step == 0)
-        expert_bytes = sparse_layers * distinct * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2 / tpw
+        expert_bytes = sparse_layers * distinct * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2 / (world if ep else tpw)
     achieved = weight_bytes / (gemm_ms * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
