@@ -510,7 +510,10 @@ def main():
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "k_gemm_dec (k_gemm_tc for the LM head): all dense weight-streaming GEMMs of one decode step",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "traffic": traffic, "algorithmic_bytes_per_sweep": weight_bytes, "launches_per_sweep": gemm_launches,
+                     "traffic": traffic,
+                     "traffic_source": ("profiles/traffic.json: one ncu capture of the decode GEMMs (dram__bytes_read.sum + "
+                                        "dram__bytes_write.sum), not measured in this run" if traffic else None),
+                     "algorithmic_bytes_per_sweep": weight_bytes, "launches_per_sweep": gemm_launches,
                      "ms_per_sweep": gemm_ms},
         "phases": {"prefill_ms": ms_prefill, "prefill_tok_s": B * S / (ms_prefill * 1e-3),
                    "decode_ms_per_step": ms_decode, "decode_tok_s": B / (ms_decode * 1e-3),

@@ -333,6 +333,7 @@ class CudaBackend(TraitBackend):
             ("cg_fused_rope", [vp, vp, f32, i64, out], i32),
             ("cg_fused_attention", [vp, vp, vp, vp, i64, f32, out], i32),
             ("cg_linear", [vp, vp, vp, out], i32),
+            ("cg_linear_glu", [vp, vp, vp, i32, out], i32),
             ("cg_fused_moe", [vp, vp, vp, vp, vp, vp, i32, i32, i32, out, out], i32),
             ("cg_randn", [vp, _c_i64p, i32, C.c_uint64, f32, f32, out], i32),
             ("cg_probe_wait_timeout", [vp], i32),
@@ -417,6 +418,10 @@ class CudaBackend(TraitBackend):
 
     def linear(self, x, w):
         return self._ext1("cg_linear", x._h, w._h)
+
+    def linear_glu(self, x, w_gate_up, act=0):
+        """act(x Wg^T) * (x Wu^T) for the stacked bf16 weight [2F, in] (cg_linear_glu)."""
+        return self._ext1("cg_linear_glu", x._h, w_gate_up._h, int(act))
 
     def peer_exchange(self):
         """(mapped, reason): whether decode-step reductions run over mapped peer memory

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libcatgrad_cuda.so")
-SOURCES = ["runtime.cu", "eager.cu", "gemm_tc.cu", "gemm_tcp.cu", "gemm_dec.cu", "fused.cu", "attention.cu", "attention_fa.cu", "attn_decode.cu", "decoder.cu", "decode_resident.cu", "safetensors.cu", "lazy.cu", "comm.cu", "moe.cu", "noalloc.cu"]
+SOURCES = ["runtime.cu", "eager.cu", "gemm_tc.cu", "gemm_tcp.cu", "gemm_tcp2.cu", "gemm_dec.cu", "fused.cu", "attention.cu", "attention_fa.cu", "attn_decode.cu", "decoder.cu", "decode_resident.cu", "safetensors.cu", "lazy.cu", "comm.cu", "moe.cu", "noalloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -113,36 +113,6 @@ struct RArgs {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_bar), "r"(rank));
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-}
-// Bounded wait on an mbarrier other CTAs of the cluster arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* cta_abort, int32_t* err) {
-  uint32_t done = 0;
-  uint64_t t0 = 0, limit = 0;
-  for (uint32_t it = 0;; ++it) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((it & 0x3FF) == 0x3FF) {
-      if (*cta_abort) return false;
-      if (*(volatile int32_t*)err == DEV_TIMEOUT) break;
-      uint64_t now = globaltimer();
-      if (t0 == 0) { t0 = now; limit = wait_limit_ns(err); }
-      else if (now - t0 > limit) break;
-    }
-  }
-  *cta_abort = 1;
-  *err = DEV_TIMEOUT;
-  return false;
-}
 // Bounded wait until the grid barrier counter reaches `target`.
 __device__ __forceinline__ bool grid_wait(const unsigned* bar, unsigned target, volatile int* cta_abort, int32_t* err) {
   uint64_t t0 = 0, limit = 0;
@@ -163,11 +133,6 @@ __device__ __forceinline__ bool grid_wait(const unsigned* bar, unsigned target, 
   return false;
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
 __device__ __forceinline__ float sum4_cluster_f32(uint32_t local_addr) {
   float v[R_CS];
 #pragma unroll

@@ -50,7 +50,18 @@ __global__ void k_embed(const uint32_t* tokens, int64_t tok_ld, int64_t tok_off,
   const int64_t b = m / S, sp = m - b * S;
   uint32_t t = tokens[b * tok_ld + tok_off + sp];
   if (t >= vocab) { if (threadIdx.x == 0) *err = DEV_INDEX; t = 0; }
-  if (st == ST_BF16) {
+  if (st == ST_BF16 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+    // eight values per thread: one 128-bit load, two 128-bit stores
+    const uint4* row = (const uint4*)((const __nv_bfloat16*)table + (int64_t)t * H);
+    float4* o = (float4*)(out + m * H);
+    for (int64_t i = threadIdx.x; i < H / 8; i += blockDim.x) {
+      const uint4 r = row[i];
+      const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&r.x), b2 = __bfloat1622float2(*(const __nv_bfloat162*)&r.y);
+      const float2 c2 = __bfloat1622float2(*(const __nv_bfloat162*)&r.z), d2 = __bfloat1622float2(*(const __nv_bfloat162*)&r.w);
+      o[2 * i] = make_float4(a.x * scale, a.y * scale, b2.x * scale, b2.y * scale);
+      o[2 * i + 1] = make_float4(c2.x * scale, c2.y * scale, d2.x * scale, d2.y * scale);
+    }
+  } else if (st == ST_BF16) {
     const __nv_bfloat162* row = (const __nv_bfloat162*)((const __nv_bfloat16*)table + (int64_t)t * H);
     float2* o = (float2*)(out + m * H);
     for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) {
@@ -446,16 +457,16 @@ __global__ void k_rope_store(RopeStoreArgs a) {
   }
 }
 
-// The same vectorised, for head sizes up to 128: one thread per four elements of a head -- for q
-// and k the rotation pairs (j, j + 1) and (j + d/2, j + d/2 + 1), for v four consecutive values
-// -- with 64-bit loads and 32-bit bf16x2 stores, contiguous across a warp.  The d/4 threads of a
-// head are consecutive lanes of one warp, so the optional per-head RMSNorm is a shuffle
-// reduction among them.
+// The same vectorised: one thread per eight elements of a head -- for q and k the rotation pairs
+// (j .. j+3) and (j + d/2 .. j + d/2 + 3), for v eight consecutive values -- with 128-bit loads
+// and 64-bit (q, k) or 128-bit (v) bf16 stores, contiguous across a warp.  The d/8 threads of a
+// head are consecutive lanes of one warp (d a multiple of 8, at most 256), so the optional
+// per-head RMSNorm is a shuffle reduction among them.
 __global__ void k_rope_store_vec(RopeStoreArgs a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int heads = a.nh + 2 * a.nkv;
-  const int d = a.d, half = d / 2, per_head = d / 4;
+  const int d = a.d, half = d / 2, per_head = d / 8;
   const int64_t total = a.M * heads * per_head;
   const int64_t pos00 = a.pos_dev ? *a.pos_dev : a.pos0;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -466,30 +477,38 @@ __global__ void k_rope_store_vec(RopeStoreArgs a) {
     const int64_t b = m / a.S, pos = pos00 + (m - b * a.S);
     const float* src = a.qkv + mh * d;
     if (h >= a.nh + a.nkv) {
-      const float4 v = ((const float4*)src)[t];
-      __nv_bfloat16* dst = a.v_cache + ((b * a.nkv + (h - a.nh - a.nkv)) * a.Tmax + pos) * d + 4 * t;
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-      *(uint2*)dst = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+      const float4 v0 = ((const float4*)src)[2 * t], v1 = ((const float4*)src)[2 * t + 1];
+      __nv_bfloat16* dst = a.v_cache + ((b * a.nkv + (h - a.nh - a.nkv)) * a.Tmax + pos) * d + 8 * t;
+      const __nv_bfloat162 p0 = __floats2bfloat162_rn(v0.x, v0.y), p1 = __floats2bfloat162_rn(v0.z, v0.w);
+      const __nv_bfloat162 p2 = __floats2bfloat162_rn(v1.x, v1.y), p3 = __floats2bfloat162_rn(v1.z, v1.w);
+      *(uint4*)dst = make_uint4(*(const uint32_t*)&p0, *(const uint32_t*)&p1, *(const uint32_t*)&p2, *(const uint32_t*)&p3);
       continue;
     }
-    const int j = 2 * t;
-    float2 x1 = *(const float2*)(src + j), x2 = *(const float2*)(src + j + half);
+    const int j = 4 * t;
+    float4 x1 = *(const float4*)(src + j), x2 = *(const float4*)(src + j + half);
     const float* gamma = h < a.nh ? a.q_gamma : a.k_gamma;
     if (gamma) {
-      float ss = x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y;
+      float ss = x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w + x2.x * x2.x + x2.y * x2.y + x2.z * x2.z + x2.w * x2.w;
       const unsigned live = __activemask();  // whole heads are in or out of range together
       for (int o = per_head / 2; o; o >>= 1) ss += __shfl_xor_sync(live, ss, o);
       const float inv = 1.f / sqrtf(ss / (float)d + a.norm_eps);
-      float2 g1 = *(const float2*)(gamma + j), g2 = *(const float2*)(gamma + j + half);
-      if (a.norm_plus_one) { g1.x += 1.f; g1.y += 1.f; g2.x += 1.f; g2.y += 1.f; }
-      x1.x = x1.x * inv * g1.x; x1.y = x1.y * inv * g1.y;
-      x2.x = x2.x * inv * g2.x; x2.y = x2.y * inv * g2.y;
+      float4 g1 = *(const float4*)(gamma + j), g2 = *(const float4*)(gamma + j + half);
+      if (a.norm_plus_one) {
+        g1.x += 1.f; g1.y += 1.f; g1.z += 1.f; g1.w += 1.f;
+        g2.x += 1.f; g2.y += 1.f; g2.z += 1.f; g2.w += 1.f;
+      }
+      x1.x = x1.x * inv * g1.x; x1.y = x1.y * inv * g1.y; x1.z = x1.z * inv * g1.z; x1.w = x1.w * inv * g1.w;
+      x2.x = x2.x * inv * g2.x; x2.y = x2.y * inv * g2.y; x2.z = x2.z * inv * g2.z; x2.w = x2.w * inv * g2.w;
     }
-    const float2 c = *(const float2*)(a.cos_t + pos * half + j), sn = *(const float2*)(a.sin_t + pos * half + j);
+    const float4 c = *(const float4*)(a.cos_t + pos * half + j), sn = *(const float4*)(a.sin_t + pos * half + j);
     __nv_bfloat16* dst = h < a.nh ? a.q_out + m * (int64_t)a.nh * d + (int64_t)h * d
                                   : a.k_cache + ((b * a.nkv + (h - a.nh)) * a.Tmax + pos) * d;
-    *(__nv_bfloat162*)(dst + j) = __floats2bfloat162_rn(c.x * x1.x - sn.x * x2.x, c.y * x1.y - sn.y * x2.y);
-    *(__nv_bfloat162*)(dst + j + half) = __floats2bfloat162_rn(c.x * x2.x + sn.x * x1.x, c.y * x2.y + sn.y * x1.y);
+    const __nv_bfloat162 l0 = __floats2bfloat162_rn(c.x * x1.x - sn.x * x2.x, c.y * x1.y - sn.y * x2.y);
+    const __nv_bfloat162 l1 = __floats2bfloat162_rn(c.z * x1.z - sn.z * x2.z, c.w * x1.w - sn.w * x2.w);
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(c.x * x2.x + sn.x * x1.x, c.y * x2.y + sn.y * x1.y);
+    const __nv_bfloat162 h1 = __floats2bfloat162_rn(c.z * x2.z + sn.z * x1.z, c.w * x2.w + sn.w * x1.w);
+    *(uint2*)(dst + j) = make_uint2(*(const uint32_t*)&l0, *(const uint32_t*)&l1);
+    *(uint2*)(dst + j + half) = make_uint2(*(const uint32_t*)&h0, *(const uint32_t*)&h1);
   }
 }
 
@@ -748,8 +767,8 @@ int k_launch_rope_tables_scaled(cg_ctx* c, float theta, const RopeScaling& rs, i
 int k_launch_rope_store(cg_ctx* c, const RopeStoreArgs& a) {
   const int64_t warps = a.M * (a.nh + 2 * a.nkv);
   if (warps == 0) return CG_OK;
-  if (a.d % 8 == 0 && ((!a.q_gamma && !a.k_gamma) || (a.q_gamma && a.k_gamma && a.d <= 128 && (128 % a.d) == 0))) {
-    const int64_t items = warps * (a.d / 4);
+  if (a.d % 8 == 0 && ((!a.q_gamma && !a.k_gamma) || (a.q_gamma && a.k_gamma && a.d <= 256 && (256 % a.d) == 0))) {
+    const int64_t items = warps * (a.d / 8);
     CG_CUDA(c, launch_kernel(c, k_rope_store_vec, dim3(grid_for(items, 256, 148 * 32)), dim3(256), 0, 1, a));
     CG_LAUNCHED(c);
     return CG_OK;
@@ -960,6 +979,39 @@ int32_t cg_linear(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, cg_tensor**
     rv.t->rank = 2; rv.t->dims[0] = M; rv.t->dims[1] = N; rv.t->strides[0] = N; rv.t->strides[1] = 1;
     CG_TRY(gemm_simt(c, xv.t, wv.t, rv.t));
   }
+  *out = r.take();
+  return CG_OK;
+}
+
+int32_t cg_linear_glu(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, int32_t act, cg_tensor** out) {
+  CG_LAZY_EAGER_SCOPE(c);
+  if (!c || !x || !w || !out) return fail(c, CG_ERR_INVALID, "null argument");
+  if (x->tag != CG_F32 || w->tag != CG_F32) return fail(c, CG_ERR_DTYPE, "linear_glu wants F32 tensors");
+  if (act != 0 && act != 1) return fail(c, CG_ERR_INVALID, "linear_glu: act is 0 (silu) or 1 (tanh gelu)");
+  if (x->rank < 1 || w->rank != 2 || x->dims[x->rank - 1] != w->dims[1] || (w->dims[0] & 1))
+    return fail(c, CG_ERR_SHAPE, "Shape mismatch in operation");
+  const int64_t K = w->dims[1], F = w->dims[0] / 2;
+  if (w->storage != ST_BF16 || !w->contiguous() || K == 0 || K % 8 || ((uintptr_t)w->data() % 16))
+    return fail(c, CG_ERR_UNSUPPORTED, "linear_glu wants a contiguous bf16-stored weight [2F, K] with K a multiple of 8");
+  const int64_t M = x->numel() / K;
+  int64_t od[CG_MAX_RANK];
+  for (int i = 0; i < x->rank; ++i) od[i] = x->dims[i];
+  od[x->rank - 1] = F;
+  Hold r;
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, od, x->rank, &r.t));
+  if (r.t->numel() == 0) { *out = r.take(); return CG_OK; }
+  Hold xc, xb;
+  CG_TRY(as_contiguous(c, x, &xc.t));
+  const __nv_bfloat16* xp;
+  if (xc.t->storage == ST_BF16) {
+    xp = (const __nv_bfloat16*)xc.t->data();
+  } else {
+    int64_t xd[2] = {M, K};
+    CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xb.t));
+    CG_TRY(k_launch_to_bf16(c, (const float*)xc.t->data(), M * K, (__nv_bfloat16*)xb.t->data()));
+    xp = (const __nv_bfloat16*)xb.t->data();
+  }
+  CG_TRY(gemm_tc_pair(c, xp, K, (const __nv_bfloat16*)w->data(), K, (__nv_bfloat16*)r.t->data(), F, M, F, K, act));
   *out = r.take();
   return CG_OK;
 }

@@ -311,6 +311,7 @@ int32_t cg_set_option(cg_ctx* c, const char* name, int64_t value) {
   }
   if (!strcmp(name, "handover")) { c->opt_handover = value != 0; return CG_OK; }
   if (!strcmp(name, "persistent")) { c->opt_persistent = value != 0; return CG_OK; }
+  if (!strcmp(name, "pair_cta")) { c->opt_pair_cta = (int)value; return CG_OK; }
   return fail(c, CG_ERR_INVALID, std::string("unknown option ") + name);
 }
 

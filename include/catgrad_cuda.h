@@ -163,6 +163,10 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "pdl"   : 1 (default) = fused kernels are launched with programmatic stream serialization
  *   "persistent" : 1 (default) = GEMMs with several output tiles per SM run as one resident
  *             CTA per SM with double-buffered accumulators; 0 = one CTA per tile
+ *   "pair_cta" : 1 = among those, GEMMs with at least two 256 x 256 tiles per SM pair run on
+ *             thread-block clusters of two CTAs (tcgen05 cta_group::2: one 256 x 256 tile per pair,
+ *             each CTA loading its own weight rows and half of the activation tile); 2 = every
+ *             tensor-core GEMM without a k split does (tests); 0 = never
  *   "handover" : 1 (default) = in decode steps of pre-norm models the residual GEMMs also leave
  *             the gain-scaled bf16 activations and per-row sums of squares, and the next GEMM
  *             applies 1 / rms in its epilogue (no separate norm kernel); 0 = norm kernels
@@ -245,6 +249,11 @@ int32_t cg_fused_attention(cg_ctx*, const cg_tensor* q, const cg_tensor* k, cons
  * (linear_no_bias, nn/mod.rs:174-199), without materialising the transpose.  Uses the
  * tcgen05 kernel when W is stored bf16. */
 int32_t cg_linear(cg_ctx*, const cg_tensor* x, const cg_tensor* w, cg_tensor** out);
+/* The gated half of an FFN in one kernel (catgrad-llm/src/models/llama.rs:24-28): for a
+ * bf16-stored weight [2F, in] whose first F rows are the gate projection and whose last F rows
+ * are the up projection, y = act(x Wg^T) * (x Wu^T), rounded once to bf16 storage.  act: 0 silu,
+ * 1 tanh gelu.  The [.., 2F] intermediate is never written. */
+int32_t cg_linear_glu(cg_ctx*, const cg_tensor* x, const cg_tensor* w, int32_t act, cg_tensor** out);
 /* A tensor of independent N(mean, std) samples generated on the device (counter-based, a
  * function of seed and element index only).  Stored like an upload of the same shape (bf16
  * for rank >= 2 under CG_PREC_BF16).  No counterpart in the reference, whose weights always

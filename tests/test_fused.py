@@ -119,6 +119,71 @@ def test_tensor_core_linear(oracle, cuda_bf16, M, N, K):
     np.testing.assert_allclose(got, simt, rtol=1e-4, atol=1e-4 * np.sqrt(K))
 
 
+# shapes with at least two 256 x 256 tiles per SM pair (the kernel's own threshold), one of them
+# ragged in every dimension, and small ones that only the forced mode sends there
+PAIR_SHAPES = [(2048, 4864, 512, 1), (1300, 9600, 520, 1), (300, 700, 192, 2), (20, 256, 64, 2), (513, 130, 1032, 2)]
+
+
+@pytest.mark.parametrize("M,N,K,mode", PAIR_SHAPES)
+def test_pair_cta_linear(oracle, cuda_bf16, M, N, K, mode):
+    """The CTA-pair GEMM (tcgen05 cta_group::2, option "pair_cta") against the f32 checker and
+    against the one-CTA kernels on the same operands."""
+    x = synth.bf16_round(rnd((M, K)))
+    w = synth.bf16_round(rnd((N, K), 0.05))
+    C = cuda_bf16
+    wt, xt = C.from_numpy(w), C.from_numpy(x)
+    base = C.to_numpy(C.linear(xt, wt))
+    C.set_option("pair_cta", mode)
+    try:
+        got = C.to_numpy(C.linear(xt, wt))
+    finally:
+        C.set_option("pair_cta", 0)
+    B = oracle
+    want = B.to_numpy(nn.linear_b_param(B, K, N, B.from_numpy(w), None, B.from_numpy(x.reshape(1, M, K)))).reshape(M, N)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4 * np.sqrt(K))
+    np.testing.assert_allclose(got, base, rtol=1e-5, atol=1e-5 * np.sqrt(K))
+
+
+def test_pair_cta_linear_exact_small_integers(cuda_bf16):
+    # integers survive bf16 and f32 accumulation exactly: any slip in which CTA holds which
+    # rows of W or which half of the tokens shows as a wrong integer
+    C = cuda_bf16
+    M, N, K = 700, 600, 192
+    x = RNG.integers(-3, 4, size=(M, K)).astype(np.float32)
+    w = RNG.integers(-3, 4, size=(N, K)).astype(np.float32)
+    C.set_option("pair_cta", 2)
+    try:
+        got = C.to_numpy(C.linear(C.from_numpy(x), C.from_numpy(w)))
+    finally:
+        C.set_option("pair_cta", 0)
+    np.testing.assert_array_equal(got, x @ w.T)
+
+
+@pytest.mark.parametrize("M,F,K,act", [(1024, 2560, 256, 0), (1100, 3000, 264, 1), (70, 96, 64, 0), (2048, 9472, 512, 0)])
+@pytest.mark.parametrize("mode", [0, 2])
+def test_linear_glu(oracle, cuda_bf16, M, F, K, act, mode):
+    """cg_linear_glu: act(x Wg^T) * (x Wu^T) in one kernel (the one-CTA kernel with two
+    accumulators, and the CTA-pair kernel with gate and up rows interleaved) against the op
+    chain of the FFN (catgrad-llm/src/models/llama.rs:24-28) on the checker; the result is
+    rounded once to bf16."""
+    x = synth.bf16_round(rnd((M, K)))
+    w = synth.bf16_round(rnd((2 * F, K), 0.05))
+    C = cuda_bf16
+    C.set_option("pair_cta", mode)
+    try:
+        y = C.linear_glu(C.from_numpy(x), C.from_numpy(w), act)
+        assert C.storage_of(y) == 2
+        got = C.to_numpy(y)
+    finally:
+        C.set_option("pair_cta", 0)
+    B = oracle
+    xb = B.from_numpy(x.reshape(1, M, K))
+    g = nn.linear_b_param(B, K, F, B.from_numpy(np.ascontiguousarray(w[:F])), None, xb)
+    u = nn.linear_b_param(B, K, F, B.from_numpy(np.ascontiguousarray(w[F:])), None, xb)
+    want = B.to_numpy(B.mul(nn.silu(B, g) if act == 0 else nn.gelu(B, g), u)).reshape(M, F)
+    np.testing.assert_allclose(got, want, rtol=2.0 ** -7, atol=1e-4)
+
+
 def test_tensor_core_linear_exact_small_integers(cuda_bf16):
     # integers survive bf16 and f32 accumulation exactly: any layout or descriptor slip shows
     C = cuda_bf16
