@@ -136,7 +136,7 @@ k_gemm_tcp2(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
   // activations, the residual and the output belong to the stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int total_tiles = p.m_tiles * p.n_tiles;
-  const int pair = blockIdx.x, pairs = gridDim.x;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -322,8 +322,9 @@ int launch_tcp2(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const T
     CG_CUDA(c, cudaFuncSetAttribute(k_gemm_tcp2<GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM));
     configured = true;
   }
-  // grid (pairs, 1, 2) in clusters of (1, 1, 2): blockIdx.x is the pair, the cluster rank the half
-  CG_CUDA(c, launch_kernel(c, k_gemm_tcp2<GLU>, dim3((unsigned)pairs, 1, 2), dim3(192), P2_SMEM, 2, mw, mx, a));
+  // clusters of (2, 1, 1): a kernel that uses cta_group::2 is refused at launch with any other
+  // pairing ("cluster misconfiguration" for clusters of (1, 1, 2)).  blockIdx.x / 2 is the pair.
+  CG_CUDA(c, launch_kernel(c, k_gemm_tcp2<GLU>, dim3(2u * (unsigned)pairs, 1, 1), dim3(192), P2_SMEM, -2, mw, mx, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }

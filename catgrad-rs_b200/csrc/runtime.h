@@ -217,7 +217,8 @@ Iter make_iter(int rank, const int64_t* dims, const int64_t* s0, const int64_t* 
 // Launch on the context's stream with programmatic dependent launch (the kernel may start
 // before its predecessor in the stream has finished; it must execute griddepcontrol.wait
 // before it reads or writes anything the predecessor touches) and, when cluster_z > 1, as
-// thread-block clusters of (1, 1, cluster_z).
+// thread-block clusters of (1, 1, cluster_z); a negative cluster_z asks for clusters of
+// (-cluster_z, 1, 1) instead (CTA pairs of tcgen05 cta_group::2 are neighbours along x).
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(cg_ctx* c, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_z,
                           Args... args) {
@@ -233,11 +234,11 @@ cudaError_t launch_kernel(cg_ctx* c, void (*kernel)(KArgs...), dim3 grid, dim3 b
     attrs[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_z > 1) {
+  if (cluster_z > 1 || cluster_z < -1) {
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.x = cluster_z < 0 ? (unsigned)-cluster_z : 1;
     attrs[n].val.clusterDim.y = 1;
-    attrs[n].val.clusterDim.z = (unsigned)cluster_z;
+    attrs[n].val.clusterDim.z = cluster_z < 0 ? 1 : (unsigned)cluster_z;
     ++n;
   }
   cfg.attrs = attrs;

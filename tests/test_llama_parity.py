@@ -160,7 +160,8 @@ def test_batch_rows_are_independent(cuda_bf16):
 def test_chunked_prefill_equals_one_chunk_and_kernel_variants_agree(cuda_bf16, cfg):
     """Size-independent properties of the prefill: processing the prompt in position chunks
     (later chunks attend to the cache with a position offset) gives the logits of one chunk, and
-    the tcgen05 attention / persistent GEMM give the logits of the mma.sync / per-tile kernels."""
+    the tcgen05 attention / persistent GEMM give the logits of the mma.sync / per-tile kernels,
+    and so do the CTA-pair GEMMs."""
     C = cuda_bf16
     batch, seq = 2, 600
     dec = cg.Decoder(C, cfg, max_seq=seq + 2, max_batch=batch)
@@ -174,12 +175,18 @@ def test_chunked_prefill_equals_one_chunk_and_kernel_variants_agree(cuda_bf16, c
         C.set_option("fa", 0)
         C.set_option("persistent", 0)
         legacy = C.to_numpy(dec.prefill(prompt, want_logits=True))
+        C.set_option("fa", 1)
+        C.set_option("persistent", 1)
+        C.set_option("pair_cta", 2)  # every prefill GEMM, gate/up included, on CTA pairs
+        paired = C.to_numpy(dec.prefill(prompt, want_logits=True))
     finally:
         C.set_option("prefill_chunk", 8192)
         C.set_option("fa", 1)
         C.set_option("persistent", 1)
+        C.set_option("pair_cta", 0)
     np.testing.assert_allclose(chunked, ref, rtol=0, atol=2e-2)
     np.testing.assert_allclose(legacy, ref, rtol=0, atol=2e-2)
+    np.testing.assert_allclose(paired, ref, rtol=0, atol=2e-2)
     dec.close()
 
 
