@@ -13,4 +13,12 @@ __device__ __forceinline__ float gelu_f(float x) {
   return 0.5f * x * (1.f + tanh_f(c * (x + 0.044715f * x * x * x)));
 }
 
+// Cheaper forms for epilogues whose result is rounded to bf16 anyway: approximate division.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_fast(float x) { return x * sigmoid_fast(x); }
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float c = 0.7978845608f;
+  return 0.5f * x * (2.f * sigmoid_fast(2.f * c * (x + 0.044715f * x * x * x)));
+}
+
 }  // namespace cg

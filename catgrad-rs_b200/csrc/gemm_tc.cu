@@ -338,7 +338,7 @@ int gemm_tc_pair(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bflo
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
     return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: k and leading dimensions must be multiples of 8, bases 16-byte aligned");
   if (M > 2147483647ll / 2 || F > 2147483647ll / 4) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tc: problem too large");
-  if (c->opt_persistent && (c->opt_pair_cta == 2 || (c->opt_pair_cta && gemm_tcp2_wanted(M, F, K, 1))))
+  if (c->opt_persistent && ((c->opt_pair_cta == 2 && gemm_tcp2_supported(F, 1)) || (c->opt_pair_cta && gemm_tcp2_wanted(M, F, K, 1))))
     return gemm_tcp2(c, x, ldx, w, ldw, 2 * F, out, ldo, nullptr, M, F, K, 1, 1, act);
   if (c->opt_persistent && gemm_tcp_wanted(M, F, K)) return gemm_tcp(c, x, ldx, w, ldw, 2 * F, out, ldo, nullptr, M, F, K, 1, 1, act);
   const int tn = M <= 128 ? 128 : 256;

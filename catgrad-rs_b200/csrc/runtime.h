@@ -92,7 +92,7 @@ struct cg_ctx {
   int opt_gemm = 0;       // 0 auto, 1 force f32 SIMT
   int opt_pdl = 1;        // programmatic dependent launch for the fused kernels
   int opt_persistent = 1; // large GEMMs take the persistent double-buffered kernel
-  int opt_pair_cta = 0;   // 1: the largest of those take the CTA-pair (cta_group::2) kernel; 2: every GEMM that reaches gemm_tc does
+  int opt_pair_cta = 1;   // 1: the largest of those take the CTA-pair (cta_group::2) kernel; 2: every GEMM that reaches gemm_tc does
   int opt_handover = 1;   // decode steps: residual GEMMs prepare the next norm, the next GEMM applies 1 / rms
   int opt_fa = 1;         // prefill attention on tcgen05 (attention_fa.cu) where it applies
   int opt_prefill_chunk = 8192;  // tokens per prefill chunk (bounds the decoder's workspace)
@@ -310,6 +310,7 @@ int gemm_tc(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16*
 // out[M, N] (bf16) = act(x gate^T) * (x up^T).  gemm_tc and gemm_tc_pair route here by themselves
 // when gemm_tcp_wanted says the problem is large enough.
 bool gemm_tcp_wanted(int64_t M, int64_t N, int64_t K);
+bool gemm_tcp2_supported(int64_t N, int glu);
 bool gemm_tcp2_wanted(int64_t M, int64_t N, int64_t K, int glu);
 int gemm_tcp2(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, int64_t ldw, int64_t w_rows, void* out,
               int64_t ldo, const float* residual, int64_t M, int64_t N, int64_t K, int out_mode, int glu, int act);

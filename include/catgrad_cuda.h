@@ -163,7 +163,7 @@ int32_t cg_to_vec_u32(cg_ctx*, const cg_tensor* x, uint32_t* dst, int64_t n);
  *   "pdl"   : 1 (default) = fused kernels are launched with programmatic stream serialization
  *   "persistent" : 1 (default) = GEMMs with several output tiles per SM run as one resident
  *             CTA per SM with double-buffered accumulators; 0 = one CTA per tile
- *   "pair_cta" : 1 = among those, GEMMs with at least two 256 x 256 tiles per SM pair run on
+ *   "pair_cta" : 1 (default) = among those, GEMMs with several 256 x 256 tiles per SM pair run on
  *             thread-block clusters of two CTAs (tcgen05 cta_group::2: one 256 x 256 tile per pair,
  *             each CTA loading its own weight rows and half of the activation tile); 2 = every
  *             tensor-core GEMM without a k split does (tests); 0 = never

@@ -119,9 +119,9 @@ def test_tensor_core_linear(oracle, cuda_bf16, M, N, K):
     np.testing.assert_allclose(got, simt, rtol=1e-4, atol=1e-4 * np.sqrt(K))
 
 
-# shapes with at least two 256 x 256 tiles per SM pair (the kernel's own threshold), one of them
+# shapes with at least four 256 x 256 tiles per SM pair (the kernel's own threshold), one of them
 # ragged in every dimension, and small ones that only the forced mode sends there
-PAIR_SHAPES = [(2048, 4864, 512, 1), (1300, 9600, 520, 1), (300, 700, 192, 2), (20, 256, 64, 2), (513, 130, 1032, 2)]
+PAIR_SHAPES = [(2048, 9728, 512, 1), (1300, 12800, 520, 1), (300, 700, 192, 2), (20, 256, 64, 2), (513, 130, 1032, 2)]
 
 
 @pytest.mark.parametrize("M,N,K,mode", PAIR_SHAPES)
@@ -132,12 +132,13 @@ def test_pair_cta_linear(oracle, cuda_bf16, M, N, K, mode):
     w = synth.bf16_round(rnd((N, K), 0.05))
     C = cuda_bf16
     wt, xt = C.from_numpy(w), C.from_numpy(x)
-    base = C.to_numpy(C.linear(xt, wt))
-    C.set_option("pair_cta", mode)
     try:
+        C.set_option("pair_cta", 0)
+        base = C.to_numpy(C.linear(xt, wt))
+        C.set_option("pair_cta", mode)
         got = C.to_numpy(C.linear(xt, wt))
     finally:
-        C.set_option("pair_cta", 0)
+        C.set_option("pair_cta", 1)
     B = oracle
     want = B.to_numpy(nn.linear_b_param(B, K, N, B.from_numpy(w), None, B.from_numpy(x.reshape(1, M, K)))).reshape(M, N)
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4 * np.sqrt(K))
@@ -155,11 +156,11 @@ def test_pair_cta_linear_exact_small_integers(cuda_bf16):
     try:
         got = C.to_numpy(C.linear(C.from_numpy(x), C.from_numpy(w)))
     finally:
-        C.set_option("pair_cta", 0)
+        C.set_option("pair_cta", 1)
     np.testing.assert_array_equal(got, x @ w.T)
 
 
-@pytest.mark.parametrize("M,F,K,act", [(1024, 2560, 256, 0), (1100, 3000, 264, 1), (70, 96, 64, 0), (2048, 9472, 512, 0)])
+@pytest.mark.parametrize("M,F,K,act", [(1024, 2560, 256, 0), (1100, 3008, 264, 1), (70, 96, 64, 0), (2048, 9472, 512, 0), (300, 1000, 128, 0)])
 @pytest.mark.parametrize("mode", [0, 2])
 def test_linear_glu(oracle, cuda_bf16, M, F, K, act, mode):
     """cg_linear_glu: act(x Wg^T) * (x Wu^T) in one kernel (the one-CTA kernel with two
@@ -175,7 +176,7 @@ def test_linear_glu(oracle, cuda_bf16, M, F, K, act, mode):
         assert C.storage_of(y) == 2
         got = C.to_numpy(y)
     finally:
-        C.set_option("pair_cta", 0)
+        C.set_option("pair_cta", 1)
     B = oracle
     xb = B.from_numpy(x.reshape(1, M, K))
     g = nn.linear_b_param(B, K, F, B.from_numpy(np.ascontiguousarray(w[:F])), None, xb)

@@ -183,7 +183,7 @@ def test_chunked_prefill_equals_one_chunk_and_kernel_variants_agree(cuda_bf16, c
         C.set_option("prefill_chunk", 8192)
         C.set_option("fa", 1)
         C.set_option("persistent", 1)
-        C.set_option("pair_cta", 0)
+        C.set_option("pair_cta", 1)
     np.testing.assert_allclose(chunked, ref, rtol=0, atol=2e-2)
     np.testing.assert_allclose(legacy, ref, rtol=0, atol=2e-2)
     np.testing.assert_allclose(paired, ref, rtol=0, atol=2e-2)
