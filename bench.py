@@ -299,13 +299,58 @@ def trait_path(cg, C, cfg, args, B, S, workload):
         ms = e0.elapsed_time(e1) / args.steps
         out[mode] = {"ms_per_job": ms, "prefill_tok_s": B * S / (ms * 1e-3), "launches_per_row": (C.launch_count() - n0) / args.steps / B,
                      "next_tokens": [int(t) for t in toks]}
+    # What the two modes disagree by (not timed): last-position logits of row 0.  On a bf16 context
+    # every GEMM input is rounded to bf16, so the last-bit differences of the fused f32 kernels
+    # flip roundings and reach the logits at the bf16 level; near-ties of a random-weight model
+    # then pick another token, which `same_next_tokens` counts without judging.
+    lg = {}
+    for mode in ("eager", "recorded"):
+        C.set_option("lazy", 1 if mode == "recorded" else 0)
+        lg[mode] = np.asarray(C.to_vec(fwd(C, cfg, params, rows[0], S, want_logits=True)[1]), dtype=np.float32).reshape(S, -1)[-1]
+    top2 = np.sort(lg["eager"])[-2:]
+    logit_cmp = {"max_abs_diff": float(np.abs(lg["eager"] - lg["recorded"]).max()), "logit_scale": float(np.abs(lg["eager"]).max()),
+                 "eager_top1_top2_margin": float(top2[1] - top2[0])}
     C.set_option("lazy", 0)
+    # Generation through the trait methods: the reference's serving loop with an explicit KV cache
+    # (catgrad-llm/src/run.rs:219-305) for ONE row -- the prompt in one call, then one token per
+    # call, the cache tensors handed from call to call.
+    gen = None
+    if cfg.arch == "llama":
+        T = min(args.decode, 32)
+        gen = {}
+        for mode in ("eager", "recorded"):
+            C.set_option("lazy", 1 if mode == "recorded" else 0)
+            res = None
+            for it in range(2):  # first pass warms up
+                runner = graphs.llama_kv.KVRunner(C, cfg, params, S + T + 8)
+                stream = iter(runner.complete([int(t) for t in prompt[0]]))
+                C.sync()
+                e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                n0 = C.launch_count()
+                e[0].record()
+                toks = [next(stream)]
+                e[1].record()
+                n1 = C.launch_count()
+                toks += [next(stream) for _ in range(T)]
+                e[2].record()
+                torch.cuda.synchronize()
+                res = {"prefill_ms": e[0].elapsed_time(e[1]), "ms_per_token": e[1].elapsed_time(e[2]) / T,
+                       "decode_tok_s": 1e3 * T / e[1].elapsed_time(e[2]), "launches_per_token": (C.launch_count() - n1) / T,
+                       "launches_prefill": n1 - n0, "tokens": toks}
+            gen[mode] = res
+        C.set_option("lazy", 0)
+        gen["same_tokens_frac"] = float(np.mean([a == b for a, b in zip(gen["eager"]["tokens"], gen["recorded"]["tokens"])]))
+        gen["what"] = f"one row: {S}-token prompt in one call, then {T} single-token calls with the cache tensors passed along"
+        for mode in ("eager", "recorded"):
+            gen[mode]["tokens"] = gen[mode]["tokens"][:8]
     print(json.dumps({
+        "generation": gen,
         "metric": "prefill tok/s through the trait methods, Llama-3.2-1B shape", "value": out["recorded"]["prefill_tok_s"], "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": out["recorded"]["ms_per_job"], "higher_is_better": True,
         "dtype": "bf16", "data": "synthetic", "config": {"workload": workload + " (prefill only, rows one at a time)", "path": "trait"},
         "eager": out["eager"], "recorded": out["recorded"],
-        "same_next_tokens": out["eager"]["next_tokens"] == out["recorded"]["next_tokens"]}))
+        "same_next_tokens": int(sum(a == b for a, b in zip(out["eager"]["next_tokens"], out["recorded"]["next_tokens"]))),
+        "rows": B, "last_position_logits_row0": logit_cmp}))
 
 
 def main():
