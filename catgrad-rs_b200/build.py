@@ -56,10 +56,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     objs = [os.path.join(OBJ, s.replace(".cu", ".o")) for s in srcs]
     if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objs, "-ldl"]
+        # link beside the library and rename: a reader (a process loading it, a copy of the tree)
+        # sees the old file or the new one, never a partly written one
+        tmp = LIB + ".tmp"
+        cmd = [NVCC, "-shared", "-ccbin", "/usr/bin/g++", "-o", tmp, *objs, "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -150,6 +150,7 @@ int32_t cg_comm_all_reduce(cg_ctx* c, cg_tensor* t) {
   if (!c->comm) return c->comm_world == 1 ? CG_OK : fail(c, CG_ERR_COMM, "communicator not initialised");
   if (t->tag != CG_F32 || !t->contiguous()) return fail(c, CG_ERR_UNSUPPORTED, "all_reduce wants a contiguous F32-tagged tensor");
   ncclDataType_t dt = t->storage == ST_BF16 ? ncclBfloat16 : ncclFloat32;
+  if (t->buf) t->buf->bf16_copy.reset();  // written in place: a cached GEMM operand copy is stale
   ncclResult_t r = nccl().AllReduce(t->data(), t->data(), (size_t)t->numel(), dt, ncclSum, (ncclComm_t)c->comm, c->core->stream);
   if (r != ncclSuccess) return fail(c, CG_ERR_COMM, std::string("ncclAllReduce: ") + nccl().GetErrorString(r));
   return CG_OK;

@@ -487,6 +487,36 @@ int as_contiguous(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
   return CG_OK;
 }
 
+int bf16_operand(cg_ctx* c, const cg_tensor* a, int64_t M, int64_t K, int64_t row_stride, int64_t col_stride, cg_tensor** keep,
+                 const __nv_bfloat16** out) {
+  *keep = nullptr;
+  if (a->storage == ST_BF16 && col_stride == 1 && row_stride == K && ((uintptr_t)a->data() % 16) == 0) {
+    *out = (const __nv_bfloat16*)a->data();
+    return CG_OK;
+  }
+  Buffer* b = a->buf.get();
+  const int64_t key[5] = {a->offset + ((int64_t)a->storage << 56), M, K, row_stride, col_stride};
+  if (b->owned && b->bf16_copy && !memcmp(b->bf16_key, key, sizeof(key))) {
+    *out = (const __nv_bfloat16*)b->bf16_copy->ptr;
+    return CG_OK;
+  }
+  int64_t xd[2] = {M, K};
+  Hold xa;
+  CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xa.t));
+  Hold av(new_view(a));
+  av.t->rank = 2;
+  av.t->dims[0] = M; av.t->dims[1] = K;
+  av.t->strides[0] = row_stride; av.t->strides[1] = col_stride;
+  CG_TRY(copy_into(c, av.t, xa.t->data(), ST_BF16, xa.t->strides));
+  *out = (const __nv_bfloat16*)xa.t->data();
+  if (b->owned) {  // (memory the library does not own may be rewritten behind its back)
+    b->bf16_copy = xa.t->buf;  // the copy lives as long as the buffer it was made from
+    memcpy(b->bf16_key, key, sizeof(key));
+  }
+  *keep = xa.take();
+  return CG_OK;
+}
+
 int as_contiguous_f32(cg_ctx* c, const cg_tensor* x, cg_tensor** out) {
   if (x->storage != ST_BF16) return as_contiguous(c, x, out);
   Hold t;
@@ -967,16 +997,11 @@ int32_t cg_matmul(cg_ctx* c, const cg_tensor* a, const cg_tensor* b, cg_tensor**
                   b->strides[rb - 2] == 1 && b->strides[rb - 1] >= K && b->strides[rb - 1] % 8 == 0 && K % 8 == 0 &&
                   ((uintptr_t)b->data() % 16 == 0);
   if (tc) {
-    int64_t xd[2] = {M, K};
+    // a as a bf16 [M, K] matrix (shared with the other GEMMs that read the same activations)
     Hold xa;
-    CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xa.t));
-    // view of a as [M, K]
-    Hold av(new_view(a));
-    av.t->rank = 2;
-    av.t->dims[0] = M; av.t->dims[1] = K;
-    av.t->strides[0] = a->strides[ra - 2]; av.t->strides[1] = a->strides[ra - 1];
-    CG_TRY(copy_into(c, av.t, xa.t->data(), ST_BF16, xa.t->strides));
-    CG_TRY(gemm_tc(c, (const __nv_bfloat16*)xa.t->data(), K, (const __nv_bfloat16*)b->data(), b->strides[rb - 1],
+    const __nv_bfloat16* xp;
+    CG_TRY(bf16_operand(c, a, M, K, a->strides[ra - 2], a->strides[ra - 1], &xa.t, &xp));
+    CG_TRY(gemm_tc(c, xp, K, (const __nv_bfloat16*)b->data(), b->strides[rb - 1],
                    r.t->data(), N, nullptr, M, N, K, 0, 0, nullptr));
   } else {
     CG_TRY(gemm_simt(c, a, b, r.t));

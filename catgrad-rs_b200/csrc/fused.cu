@@ -960,14 +960,7 @@ int32_t cg_linear(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, cg_tensor**
     Hold xc, xb;
     CG_TRY(as_contiguous(c, x, &xc.t));
     const __nv_bfloat16* xp;
-    if (xc.t->storage == ST_BF16) {
-      xp = (const __nv_bfloat16*)xc.t->data();
-    } else {
-      int64_t xd[2] = {M, K};
-      CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xb.t));
-      CG_TRY(k_launch_to_bf16(c, (const float*)xc.t->data(), M * K, (__nv_bfloat16*)xb.t->data()));
-      xp = (const __nv_bfloat16*)xb.t->data();
-    }
+    CG_TRY(bf16_operand(c, xc.t, M, K, K, 1, &xb.t, &xp));
     CG_TRY(gemm_tc(c, xp, K, (const __nv_bfloat16*)w->data(), K, r.t->data(), N, nullptr, M, N, K, 0, 0, nullptr));
   } else {
     // [1, M, K] x [1, K, N] through strided views, like linear_b_param's transpose + reshape
@@ -1003,14 +996,7 @@ int32_t cg_linear_glu(cg_ctx* c, const cg_tensor* x, const cg_tensor* w, int32_t
   Hold xc, xb;
   CG_TRY(as_contiguous(c, x, &xc.t));
   const __nv_bfloat16* xp;
-  if (xc.t->storage == ST_BF16) {
-    xp = (const __nv_bfloat16*)xc.t->data();
-  } else {
-    int64_t xd[2] = {M, K};
-    CG_TRY(new_tensor(c, CG_F32, ST_BF16, xd, 2, &xb.t));
-    CG_TRY(k_launch_to_bf16(c, (const float*)xc.t->data(), M * K, (__nv_bfloat16*)xb.t->data()));
-    xp = (const __nv_bfloat16*)xb.t->data();
-  }
+  CG_TRY(bf16_operand(c, xc.t, M, K, K, 1, &xb.t, &xp));
   CG_TRY(gemm_tc_pair(c, xp, K, (const __nv_bfloat16*)w->data(), K, (__nv_bfloat16*)r.t->data(), F, M, F, K, act));
   *out = r.take();
   return CG_OK;

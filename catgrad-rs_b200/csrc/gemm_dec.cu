@@ -12,9 +12,13 @@
 //   * warp 1 issues tcgen05.mma (128 x TN x 16, f32 accumulators in TMEM).  For the gate/up
 //     pair of the FFN both 128-row tiles share the CTA and the epilogue writes
 //     act(gate) * up directly (llama.rs:27), so the [M, 2F] intermediate never exists.
-//   * split-K partials are summed in rank order over distributed shared memory inside a
-//     thread-block cluster (deterministic), then the epilogue (residual add / bf16 / act)
-//     is applied once.
+//   * split-K partials are PUSHED over distributed shared memory inside a thread-block cluster:
+//     every CTA stores its partial rows into the exchange area of the CTA that finishes them,
+//     one cluster barrier makes the stores visible, and the owner adds the partials in rank
+//     order (deterministic) out of its own shared memory and applies the epilogue (residual add /
+//     bf16 / act) once.  No CTA reads another's memory, so none has to wait for the others
+//     before it leaves; the residual of the element a thread will finish is fetched while the
+//     MMAs still run.
 //
 //   * two optional hand-overs ride on the epilogue.  Norm hand-over: a residual GEMM also
 //     leaves bf16(out * gain) and per-CTA sums of out^2, and the GEMM behind the norm applies
@@ -46,6 +50,7 @@ struct DecArgs {
   int dual, act, up_off;
   int M, N, K;
   int kb_total, kb_per_split, splits, stages;
+  int xstage_cols;  // split-K: token columns of the exchange area (>= min(TN, M)); 0 without split-K
   int32_t* err;
   int trace;  // slot in the timeline buffer, or -1
   PeerPush push;  // out_mode 3
@@ -75,7 +80,13 @@ __device__ __forceinline__ void trace_max(int slot, int f) {
   if (slot >= 0) atomicMax(&g_trace[slot * 4 + f], (unsigned long long)globaltimer());
 }
 
-__device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g, float u, uint32_t parity, const float* sc) {
+// `pre` (optional): the residual and next-norm gain of this element, fetched before the accumulator was ready
+struct Prefetched {
+  bool have;
+  float res, gain;
+};
+__device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g, float u, uint32_t parity, const float* sc,
+                                        const Prefetched pre = Prefetched{false, 0.f, 0.f}) {
   if (p.ss_in) {  // the activations were handed over un-normalised: the row's 1 / rms goes here
     g *= sc[m];
     u *= sc[m];
@@ -86,9 +97,10 @@ __device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g,
   if (p.xb_out) {
     // residual epilogue that also prepares the next norm: the new residual in f32, its
     // gain-scaled bf16 copy for the next GEMM, and its square for the row's sum of squares
-    const float r = v + p.residual[o];
+    const float r = v + (pre.have ? pre.res : p.residual[o]);
     ((float*)p.out)[o] = r;
-    const float gn = p.g_plus_one ? 1.f + p.g_next[n] : p.g_next[n];
+    const float gw = pre.have ? pre.gain : p.g_next[n];
+    const float gn = p.g_plus_one ? 1.f + gw : gw;
     p.xb_out[o] = __float2bfloat16_rn(r * gn);
     return r * r;
   }
@@ -100,7 +112,7 @@ __device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g,
   }
   if (p.out_mode == 0) ((float*)p.out)[o] = v;
   else if (p.out_mode == 1) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
-  else ((float*)p.out)[o] = v + p.residual[o];
+  else ((float*)p.out)[o] = v + (pre.have ? pre.res : p.residual[o]);
   return 0.f;
 }
 
@@ -117,15 +129,19 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   const int STAGES = p.stages;
   const uint32_t wbytes = p.dual ? 2 * A_BYTES : A_BYTES;
   const uint32_t stage_bytes = wbytes + X_TILE;
-  const uint32_t boff = STAGES * stage_bytes;
+  // split-K exchange area [splits][(1 + dual) * xstage_cols][128 / splits] f32 behind the ring (NOT inside
+  // it: the other CTAs of the cluster write here while this CTA may still be streaming)
+  const uint32_t xbytes = (uint32_t)((p.dual ? 2 : 1) * p.xstage_cols) * BM * 4u;
+  const uint32_t xoff = STAGES * stage_bytes;
+  const uint32_t boff = xoff + xbytes;
   const uint32_t bars = base + boff;  // full[STAGES], empty[STAGES], accum
   const uint32_t bar_accum = bars + 16 * STAGES;
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen + boff + 16 * STAGES + 8);
   volatile int* cta_abort = (volatile int*)(gen + boff + 16 * STAGES + 12);
   float* sc = (float*)(gen + boff + 16 * 8 + 64);  // [32] per-token 1 / rms (consumer side)
-  // [SQ_FLOATS] squared outputs (producer side): in the ring, which is idle by then, behind the
-  // staging area of the cluster reduction
-  float* sq = (float*)(gen + 2 * TN * BM * 4);
+  // [SQ_FLOATS] squared outputs (producer side): in the ring, which is idle by then (only this
+  // CTA touches its ring)
+  float* sq = (float*)gen;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BM, split = blockIdx.z;
@@ -156,6 +172,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   const uint32_t tmem_acc = *tmem_slot;
 
   bool acc_ok = false;
+  Prefetched pre{false, 0.f, 0.f};
   if (warp == 0) {
     if (lane == 0 && nkb > 0) {
       // weights first: they do not depend on the preceding kernel
@@ -211,6 +228,21 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   } else {
     // outputs (and the residual) belong to the stream order: wait for the preceding kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.splits > 1 && (p.out_mode == 2 || p.xb_out)) {
+      // split-K: the element this thread will finish first is known now; fetch its residual (and
+      // the next norm's gain) while the MMAs run instead of after the reduction
+      const int rows_per = BM / p.splits;
+      const int e = tid - 64;
+      if (e < rows_per * min(TN, p.M)) {
+        const int col = e / rows_per;
+        const int n = n0 + split * rows_per + (e - col * rows_per);
+        if (n < p.N) {
+          asm volatile("ld.global.f32 %0, [%1];" : "=f"(pre.res) : "l"(p.residual + (int64_t)col * p.ldo + n) : "memory");
+          if (p.xb_out) asm volatile("ld.global.f32 %0, [%1];" : "=f"(pre.gain) : "l"(p.g_next + n) : "memory");
+          pre.have = true;
+        }
+      }
+    }
     if (p.ss_in) {
       // per-token sum of squares = the producer's per-CTA partials added in a fixed order
       // (four interleaved quarters per token, then the quarters): loads fly while the MMAs run
@@ -239,7 +271,15 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const int n = n0 + row;
-    float* stage = (float*)gen;  // [2][TN][128] partial tiles; the ring is idle by now
+    // split-K: every value goes straight into the exchange area of the CTA that finishes its row
+    // (rows [r * 128 / S, (r + 1) * 128 / S) belong to cluster rank r), slot [this split][col][row]
+    const int rows_per = BM / p.splits;
+    const int xcols = (p.dual ? 2 : 1) * p.xstage_cols;
+    uint32_t xdst = 0;
+    if (cluster) {
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(xdst) : "r"(base + xoff), "r"((uint32_t)(row / rows_per)));
+      xdst += (uint32_t)(split * xcols * rows_per + row % rows_per) * 4u;
+    }
 #pragma unroll 1
     for (int c0 = 0; c0 < TN; c0 += 16) {
       if (c0 >= p.M) break;
@@ -250,8 +290,11 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
       if (cluster) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          stage[(c0 + j) * BM + row] = __uint_as_float(g[j]);
-          if (p.dual) stage[(TN + c0 + j) * BM + row] = __uint_as_float(u[j]);
+          if (c0 + j >= p.M) break;
+          asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(xdst + (uint32_t)((c0 + j) * rows_per) * 4u), "r"(g[j]) : "memory");
+          if (p.dual)
+            asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(xdst + (uint32_t)((p.xstage_cols + c0 + j) * rows_per) * 4u), "r"(u[j])
+                         : "memory");
         }
       } else {
 #pragma unroll
@@ -276,20 +319,32 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   }
 
   if (cluster) {
+    // One cluster barrier: every CTA's pushes are visible after it, and nobody touches another
+    // CTA's shared memory again, so a CTA may leave as soon as its own rows are finished.
     __syncwarp();
     cluster_sync_all();
     if (warp >= 2 && !*cta_abort) {
       const int S = p.splits;
       const int rows_per = BM / S;
       const int cols = min(TN, p.M);
+      const int xcols = (p.dual ? 2 : 1) * p.xstage_cols;
+      const float* xs = (const float*)(gen + xoff);
       for (int e = tid - 64; e < rows_per * cols; e += 128) {
-        const int col = e / rows_per;
-        const int row = split * rows_per + (e - col * rows_per);
-        const float g = sum_cluster_f32(base + (uint32_t)(col * BM + row) * 4u, S);
-        const float u = p.dual ? sum_cluster_f32(base + (uint32_t)((TN + col) * BM + row) * 4u, S) : 0.f;
+        const int col = e / rows_per, rl = e - col * rows_per;
+        const int row = split * rows_per + rl;
+        // the splits' partial sums in rank order (all loads first)
+        float pg[16], pu[16];
+#pragma unroll
+        for (int s = 0; s < 16; ++s) {
+          pg[s] = s < S ? xs[(s * xcols + col) * rows_per + rl] : 0.f;
+          pu[s] = (p.dual && s < S) ? xs[(s * xcols + p.xstage_cols + col) * rows_per + rl] : 0.f;
+        }
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int s = 0; s < 16; ++s) { g += pg[s]; u += pu[s]; }  // the zeros of absent ranks change nothing
         const int n = n0 + row;
         float r2 = 0.f;
-        if (n < p.N) r2 = finish(p, col, n, g, u, parity, sc);
+        if (n < p.N) r2 = finish(p, col, n, g, u, parity, sc, e == tid - 64 ? pre : Prefetched{false, 0.f, 0.f});
         if (p.ss_out) sq[e] = r2;  // e = col * rows_per + local row
       }
       if (p.ss_out) {
@@ -302,8 +357,6 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
         }
       }
     }
-    __syncwarp();
-    cluster_sync_all();
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -365,14 +418,18 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   // (and prefetching their weights) while this one computes
   // (the paired gate/up GEMM carries two weight tiles per stage, so the same budget would
   // leave it only two stages: it gets three, at two CTAs per SM)
-  const size_t budget = g.dual ? (tn == 32 ? 110 : 104) * 1024 : 72 * 1024;
-  int stages = (int)std::max<size_t>(2, budget / stage);
+  // The split-K exchange area (written by the other CTAs of the cluster, so outside the ring)
+  // comes out of the same budget: three CTAs per SM may use 75 KB each, two 113 KB each.
+  const int xstage_cols = splits > 1 ? (int)std::min<int64_t>(tn, g.M) : 0;
+  const size_t xbytes = (size_t)(g.dual ? 2 : 1) * xstage_cols * BM * 4;
+  const size_t fixed = 1024 + 16 * 8 + 64 + 128;
+  const size_t budget = (g.dual ? 113 * 1024 : 75 * 1024) - fixed;
+  int stages = (int)std::max<size_t>(2, (budget > xbytes ? budget - xbytes : 0) / stage);
   stages = std::min(stages, std::max(kb_per, 2));
   stages = std::min(stages, 8);
-  // cluster-reduce staging and the squared-output staging of the norm hand-over live in the ring
-  const size_t stage_need = (size_t)2 * tn * BM * 4 + (g.ss_out ? (size_t)SQ_FLOATS * 4 : 0);
-  while ((splits > 1 || g.ss_out) && stage_need > (size_t)stages * stage) ++stages;
-  const size_t smem = (size_t)stages * stage + 1024 + 16 * 8 + 64 + 128;
+  // the squared-output staging of the norm hand-over lives in the ring
+  while (g.ss_out && (size_t)SQ_FLOATS * 4 > (size_t)stages * stage) ++stages;
+  const size_t smem = (size_t)stages * stage + xbytes + fixed;
 
   CUtensorMap mw, mx;
   CG_TRY(make_map(c, &mw, g.w, g.w_rows, g.K, g.ldw, BM));
@@ -382,6 +439,7 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   a.dual = g.dual; a.act = g.act; a.up_off = (int)g.N;
   a.M = (int)g.M; a.N = (int)g.N; a.K = (int)g.K;
   a.kb_total = kb_total; a.kb_per_split = kb_per; a.splits = splits; a.stages = stages;
+  a.xstage_cols = xstage_cols;
   a.err = c->core->dev_err;
   a.trace = c->trace_on ? (int)(c->trace_next++ % TRACE_SLOTS) : -1;
   a.total_ctas = (int)(tiles * splits);

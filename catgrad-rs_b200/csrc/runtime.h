@@ -35,6 +35,12 @@ struct Buffer {
   void* ptr = nullptr;
   size_t bytes = 0;   // size of the underlying block
   bool owned = true;  // false: memory belongs to someone else (never freed here)
+  // The last bf16-rounded copy made of (a view of) this buffer as a GEMM operand, with the view
+  // it was made for: q, k and v (or gate and up) read the same activations, and trait tensors
+  // are never written after they are made, so the copy serves every one of them.  Whoever does
+  // write a tensor in place (cg_comm_all_reduce) drops it.
+  std::shared_ptr<Buffer> bf16_copy;
+  int64_t bf16_key[5] = {0, 0, 0, 0, 0};  // offset, rows, cols, row stride, col stride
   ~Buffer();
 };
 
@@ -201,6 +207,12 @@ struct Hold {
 
 // A contiguous tensor equal to x: x itself (retained) when already contiguous.
 int as_contiguous(cg_ctx* c, const cg_tensor* x, cg_tensor** out);
+// The [M, K] matrix that the last two axes of `a` (all leading axes folded into M; `a` must be
+// contiguous over them, or rank 2) form, as a contiguous bf16 matrix: `a` itself when it is stored
+// that way, else the rounded copy cached on its buffer (made on first use).  *keep holds whatever
+// must stay alive while the pointer is used.
+int bf16_operand(cg_ctx* c, const cg_tensor* a, int64_t M, int64_t K, int64_t row_stride, int64_t col_stride, cg_tensor** keep,
+                 const __nv_bfloat16** out);
 // Like as_contiguous but also widens bf16 storage to f32.
 int as_contiguous_f32(cg_ctx* c, const cg_tensor* x, cg_tensor** out);
 

@@ -185,6 +185,30 @@ def test_linear_glu(oracle, cuda_bf16, M, F, K, act, mode):
     np.testing.assert_allclose(got, want, rtol=2.0 ** -7, atol=1e-4)
 
 
+def test_bf16_operand_is_rounded_once_for_all_its_readers(cuda_bf16):
+    """q, k and v (or gate and up) read the same activations: the bf16 copy a tensor-core GEMM
+    makes of them is kept with the tensor and serves the later GEMMs, through `linear` and
+    through the trait's matmul on a transposed weight alike; results are unchanged."""
+    C = cuda_bf16
+    M, K, N = 96, 256, 384
+    x = rnd((1, M, K))
+    w1, w2 = synth.bf16_round(rnd((N, K), 0.05)), synth.bf16_round(rnd((N, K), 0.05))
+    t1, t2 = C.from_numpy(w1), C.from_numpy(w2)
+    x0 = C.from_numpy(x)
+    xt = C.add(x0, x0)  # a computed tensor is stored f32 (an upload of rank >= 2 would be bf16 already)
+    assert C.storage_of(xt) == 0
+    n0 = C.launch_count()
+    a = C.to_numpy(C.linear(xt, t1))
+    n1 = C.launch_count()
+    b = C.to_numpy(nn.linear_b_param(C, K, N, t2, None, xt))
+    n2 = C.launch_count()
+    fresh = C.to_numpy(C.linear(C.add(x0, x0), t2))
+    np.testing.assert_array_equal(b, fresh)
+    assert (n1 - n0) - (n2 - n1) == 1  # the first GEMM rounds the activations, the second does not
+    xb = 2 * synth.bf16_round(x)
+    np.testing.assert_allclose(a, (xb.reshape(M, K) @ w1.T).reshape(1, M, N), rtol=1e-4, atol=1e-3)
+
+
 def test_tensor_core_linear_exact_small_integers(cuda_bf16):
     # integers survive bf16 and f32 accumulation exactly: any layout or descriptor slip shows
     C = cuda_bf16
