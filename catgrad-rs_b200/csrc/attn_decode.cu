@@ -39,16 +39,29 @@ struct KernelEnv {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
   __device__ __forceinline__ uint32_t cluster_rank(int s) const { return (uint32_t)s; }
+  // the projected row, and the position when it lives on the device, belong to the stream order
+  const AttnDecArgs* args;
+  __device__ __forceinline__ int64_t settle(int64_t) const {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    return args->pos_dev ? *(const volatile int64_t*)args->pos_dev : args->pos0;
+  }
 };
 
 template <int D>
 __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ __align__(16) uint8_t smem[];
   KernelEnv env;
-  const int64_t pos = a.pos_dev ? *a.pos_dev : a.pos0;
-  attn_dec_item<D>(a, scale, (int)blockIdx.x, (int64_t)blockIdx.y, (int)blockIdx.z, pos, smem, env);
+  env.args = &a;
+  // Before the dependency wait: the first tiles of cached keys and values can be on the way
+  // while the projection GEMM still runs.  What makes that sound: every writer of the device-side
+  // position (the one-thread state kernel, in plain stream order; the arg-max kernel, after its
+  // own dependency wait) stores a value v only after every kernel that wrote cache rows below v
+  // has completed, so whatever value is visible here, the rows below it are complete.  The value
+  // may be a step old; it is re-read after the wait and a changed value repeats the request.
+  int64_t pos_early = a.pos_dev ? *(const volatile int64_t*)a.pos_dev : a.pos0;
+  pos_early = pos_early < 0 ? 0 : (pos_early >= a.Tmax ? a.Tmax - 1 : pos_early);
+  attn_dec_item<D>(a, scale, (int)blockIdx.x, (int64_t)blockIdx.y, (int)blockIdx.z, pos_early, smem, env);
 }
 
 template <int D>

@@ -9,6 +9,10 @@
 //   sync_group()     barrier among the CTAs that hold the slices of one (row, kv head),
 //                    including a barrier among each CTA's own 128 threads
 //   cluster_rank(s)  cluster rank of the CTA that holds slice s
+//   settle(pos)      called once the first K/V tiles have been requested with a position that may
+//                    be one step old: waits for whatever the caller's inputs depend on and returns
+//                    the position to use (cached keys never change, so an early request is either
+//                    right or is repeated)
 #pragma once
 
 #include "kernels.h"
@@ -36,7 +40,7 @@ __host__ __device__ constexpr size_t attn_dec_smem_bytes() {
 // KT = keys per warp tile: 32, or 16 for head size 256 so that a CTA's tiles fit a third of an
 // SM's shared memory.
 template <int D, class Env>
-__device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale, int kvh, int64_t b, int split, int64_t pos,
+__device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale, int kvh, int64_t b, int split, int64_t pos_early,
                                               uint8_t* smem, Env& env) {
   constexpr int KT = D > 128 ? 16 : 32;
   constexpr int MAX_REP = ATTN_MAX_REP;
@@ -63,12 +67,17 @@ __device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale,
   __nv_bfloat16* vbase = a.v_cache + ((b * a.nkv + kvh) * a.Tmax) * (int64_t)D;
 
   // this CTA's slice of the cached keys [lo, pos)
-  int64_t lo = 0;
-  if (a.window > 0) lo = max((int64_t)0, pos - a.window + 1);
-  const int64_t span = pos - lo;
-  int64_t per = (span + a.splits - 1) / a.splits;
-  per = (per + KT - 1) / KT * KT;
-  const int64_t t0 = lo + split * per, t1 = min(pos, t0 + per);
+  int64_t pos = pos_early, t0 = 0, t1 = 0;
+  auto plan = [&]() {
+    int64_t lo = 0;
+    if (a.window > 0) lo = max((int64_t)0, pos - a.window + 1);
+    const int64_t span = pos - lo;
+    int64_t per = (span + a.splits - 1) / a.splits;
+    per = (per + KT - 1) / KT * KT;
+    t0 = lo + split * per;
+    t1 = min(pos, t0 + per);
+  };
+  plan();
 
   __nv_bfloat16* kw = kt + (size_t)warp * KT * LD;
   __nv_bfloat16* vw = vt + (size_t)warp * KT * LD;
@@ -90,6 +99,17 @@ __device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale,
   };
   int64_t c0 = t0 + warp * KT;
   if (c0 < t1) request(c0);
+  {
+    const int64_t pos_now = env.settle(pos);
+    if (pos_now != pos) {  // the early position was stale: let the copies land, then ask again
+      cp_async_wait_all();
+      __syncwarp();
+      pos = pos_now;
+      plan();
+      c0 = t0 + warp * KT;
+      if (c0 < t1) request(c0);
+    }
+  }
 
   // ---- 1. q, k, v of the new token ----
   const int heads = a.nh + 2 * a.nkv;

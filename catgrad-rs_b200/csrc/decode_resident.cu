@@ -204,6 +204,7 @@ struct ResidentAttnEnv {
     phase ^= 1u;
   }
   __device__ __forceinline__ uint32_t cluster_rank(int s) const { return (uint32_t)(base + s); }
+  __device__ __forceinline__ int64_t settle(int64_t pos) const { return pos; }  // the phase barrier came first
 };
 
 template <int TN, int D>

@@ -30,6 +30,7 @@
 // All waits are bounded; on expiry the context's error word is raised and the kernel still
 // passes its cluster barriers, frees its TMEM and returns.
 #include <algorithm>
+#include <cstdlib>
 
 #include "act.cuh"
 #include "kernels.h"
@@ -391,8 +392,12 @@ bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 
 // split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this GPU
 // supports), at most about three CTAs per SM in total, at least two k blocks per CTA
 static int dec_splits(int64_t tiles, int kb_total) {
+  static const int cap = [] {
+    const char* e = getenv("CG_DEC_CTA_CAP");  // experiments: total CTAs a decode GEMM may use
+    return e && atoi(e) > 0 ? atoi(e) : 3 * 148;
+  }();
   int splits = 1;
-  while (splits < 16 && tiles * (splits * 2) <= 3 * 148 && kb_total / (splits * 2) >= 2) splits *= 2;
+  while (splits < 16 && tiles * (splits * 2) <= cap && kb_total / (splits * 2) >= 2) splits *= 2;
   const int kb_per = (kb_total + splits - 1) / splits;
   if ((kb_total + kb_per - 1) / kb_per != splits) splits = 1;  // an empty slice would break the cluster shape
   return splits;

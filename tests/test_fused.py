@@ -119,7 +119,7 @@ def test_tensor_core_linear(oracle, cuda_bf16, M, N, K):
     np.testing.assert_allclose(got, simt, rtol=1e-4, atol=1e-4 * np.sqrt(K))
 
 
-# shapes with at least four 256 x 256 tiles per SM pair (the kernel's own threshold), one of them
+# shapes above the kernel's own threshold (one and a half 256 x 256 tiles per SM pair), one of them
 # ragged in every dimension, and small ones that only the forced mode sends there
 PAIR_SHAPES = [(2048, 9728, 512, 1), (1300, 12800, 520, 1), (300, 700, 192, 2), (20, 256, 64, 2), (513, 130, 1032, 2)]
 
