@@ -30,7 +30,6 @@
 // All waits are bounded; on expiry the context's error word is raised and the kernel still
 // passes its cluster barriers, frees its TMEM and returns.
 #include <algorithm>
-#include <cstdlib>
 
 #include "act.cuh"
 #include "kernels.h"
@@ -117,8 +116,10 @@ __device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g,
   return 0.f;
 }
 
-template <int TN>
-__global__ void __launch_bounds__(192, 3)
+// OCC: CTAs per SM the register allocation must allow (the fewer registers a CTA holds, the
+// sooner the CTAs of the NEXT kernels in the stream fit beside it and start fetching their weights)
+template <int TN, int OCC>
+__global__ void __launch_bounds__(192, OCC)
 k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, DecArgs p) {
   constexpr uint32_t X_TILE = TN * BK * 2;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -371,16 +372,16 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   if (tid == 0) trace_max(p.trace, 3);
 }
 
-template <int TN>
+template <int TN, int OCC>
 int launch_dec(cg_ctx* c, const CUtensorMap& mw, const CUtensorMap& mx, const DecArgs& a, dim3 grid, size_t smem) {
   static PerDeviceSize configured_on;
   size_t& configured = configured_on.at(c->core->device);
   if (smem > configured) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CG_CUDA(c, cudaFuncSetAttribute(k_gemm_dec<TN, OCC>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     configured = smem;
   }
-  CG_CUDA(c, launch_kernel(c, k_gemm_dec<TN>, grid, dim3(192), smem, a.splits, mw, mx, a));
+  CG_CUDA(c, launch_kernel(c, k_gemm_dec<TN, OCC>, grid, dim3(192), smem, a.splits, mw, mx, a));
   CG_LAUNCHED(c);
   return CG_OK;
 }
@@ -392,10 +393,8 @@ bool gemm_dec_supported(int64_t M, int64_t K) { return M >= 1 && M <= 32 && K % 
 // split-K: a power of two up to 16 (one cluster; above 8 is the non-portable size this GPU
 // supports), at most about three CTAs per SM in total, at least two k blocks per CTA
 static int dec_splits(int64_t tiles, int kb_total) {
-  static const int cap = [] {
-    const char* e = getenv("CG_DEC_CTA_CAP");  // experiments: total CTAs a decode GEMM may use
-    return e && atoi(e) > 0 ? atoi(e) : 3 * 148;
-  }();
+  // (caps of 300 / 222 / 160 CTAs were measured 0.5 / 9 / 13 % slower per decode step, 600 4 % slower)
+  const int cap = 3 * 148;
   int splits = 1;
   while (splits < 16 && tiles * (splits * 2) <= cap && kb_total / (splits * 2) >= 2) splits *= 2;
   const int kb_per = (kb_total + splits - 1) / splits;
@@ -428,6 +427,7 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   const int xstage_cols = splits > 1 ? (int)std::min<int64_t>(tn, g.M) : 0;
   const size_t xbytes = (size_t)(g.dual ? 2 : 1) * xstage_cols * BM * 4;
   const size_t fixed = 1024 + 16 * 8 + 64 + 128;
+  // (smaller budgets -- 57 or 43 KB, 78 KB for the pair -- were measured 2-5 % slower per step)
   const size_t budget = (g.dual ? 113 * 1024 : 75 * 1024) - fixed;
   int stages = (int)std::max<size_t>(2, (budget > xbytes ? budget - xbytes : 0) / stage);
   stages = std::min(stages, std::max(kb_per, 2));
@@ -460,8 +460,10 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
     a.push = PeerPush{};
   }
   dim3 grid((unsigned)tiles, 1, (unsigned)splits);
-  if (tn == 16) return launch_dec<16>(c, mw, mx, a, grid, smem);
-  return launch_dec<32>(c, mw, mx, a, grid, smem);
+  // (register bound for 4 CTAs per SM: 0.861 -> 0.836 ms per Llama-3.2-1B decode step against a
+  // bound for 3; bounds for 5 and 6 measured the same as 4)
+  if (tn == 16) return launch_dec<16, 4>(c, mw, mx, a, grid, smem);
+  return launch_dec<32, 4>(c, mw, mx, a, grid, smem);
 }
 
 }  // namespace cg
