@@ -242,13 +242,13 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       uint32_t va[32], vb[32];
       // pass 1: row maximum of the visible scores.  The loads are double-buffered: chunk c+1 is
       // in flight while chunk c is reduced.
-      // (the chunk loops of both passes run rolled, two chunks -- the two register buffers -- per
-      // iteration: fully unrolled, the softmax code pushes the single-thread TMA and MMA loops
-      // out of the instruction cache)
       float mx = -INFINITY;
       tmem_ld32(s_addr, va);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      auto max_chunk = [&](const uint32_t* cur, uint32_t* nxt, int c) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
         if (c + 1 < NCH) tmem_ld32(s_addr + (uint32_t)(c + 1) * 32u, nxt);
         if (!diag) {
 #pragma unroll
@@ -259,11 +259,6 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
           for (int i = 0; i < 32; ++i) mx = i <= rel ? fmaxf(mx, __uint_as_float(cur[i])) : mx;
         }
         if (c + 1 < NCH) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      };
-#pragma unroll 1
-      for (int c = 0; c < NCH; c += 2) {
-        max_chunk(va, vb, c);
-        max_chunk(vb, va, c + 1);
       }
       const float m_new = fmaxf(m, mx);
       const float m_safe = m_new == -INFINITY ? 0.f : m_new;
@@ -278,7 +273,10 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       float ls = 0.f;
       tmem_ld32(s_addr, va);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      auto exp_chunk = [&](const uint32_t* cur, uint32_t* nxt, int c) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
         if (c + 1 < NCH) tmem_ld32(s_addr + (uint32_t)(c + 1) * 32u, nxt);
         const int rel = lim - c * 32;
         uint32_t pk[16];
@@ -304,11 +302,6 @@ k_attn_fa(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
                        : "memory");
         }
         if (c + 1 < NCH) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      };
-#pragma unroll 1
-      for (int c = 0; c < NCH; c += 2) {
-        exp_chunk(va, vb, c);
-        exp_chunk(vb, va, c + 1);
       }
       // S buffer free for the tile after next; P visible to the tensor core
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
