@@ -50,7 +50,10 @@ struct DecArgs {
   int dual, act, up_off;
   int M, N, K;
   int kb_total, kb_per_split, splits, stages;
+  int x_rows;       // activation rows per k block in the ring (8 or TN)
   int xstage_cols;  // split-K: token columns of the exchange area (>= min(TN, M)); 0 without split-K
+  int xstage_in_ring;  // the exchange area lies over the ring (more than 16 tokens: it would cost the ring a
+                       // stage): then a first cluster barrier says every CTA's ring is idle before anyone pushes
   int32_t* err;
   int trace;  // slot in the timeline buffer, or -1
   PeerPush push;  // out_mode 3
@@ -121,7 +124,9 @@ __device__ __forceinline__ float finish(const DecArgs& p, int m, int n, float g,
 template <int TN, int OCC>
 __global__ void __launch_bounds__(192, OCC)
 k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, DecArgs p) {
-  constexpr uint32_t X_TILE = TN * BK * 2;
+  // activation rows fetched per k block: TN, or 8 for up to 8 tokens (the MMA still reads TN rows;
+  // the rows past the 8th are whatever follows in shared memory and feed only unused columns)
+  const uint32_t X_TILE = (uint32_t)p.x_rows * BK * 2;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   extern __shared__ uint8_t smem_raw[];
@@ -131,11 +136,12 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   const int STAGES = p.stages;
   const uint32_t wbytes = p.dual ? 2 * A_BYTES : A_BYTES;
   const uint32_t stage_bytes = wbytes + X_TILE;
-  // split-K exchange area [splits][(1 + dual) * xstage_cols][128 / splits] f32 behind the ring (NOT inside
-  // it: the other CTAs of the cluster write here while this CTA may still be streaming)
+  // split-K exchange area [splits][(1 + dual) * xstage_cols][128 / splits] f32.  Up to 16 tokens it lies
+  // behind the ring (not inside it: the other CTAs of the cluster write here while this CTA may
+  // still be streaming); above, inside the ring, guarded by one more cluster barrier.
   const uint32_t xbytes = (uint32_t)((p.dual ? 2 : 1) * p.xstage_cols) * BM * 4u;
-  const uint32_t xoff = STAGES * stage_bytes;
-  const uint32_t boff = xoff + xbytes;
+  const uint32_t xoff = p.xstage_in_ring ? 0u : STAGES * stage_bytes;
+  const uint32_t boff = STAGES * stage_bytes + (p.xstage_in_ring ? 0u : xbytes);
   const uint32_t bars = base + boff;  // full[STAGES], empty[STAGES], accum
   const uint32_t bar_accum = bars + 16 * STAGES;
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen + boff + 16 * STAGES + 8);
@@ -143,7 +149,7 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   float* sc = (float*)(gen + boff + 16 * 8 + 64);  // [32] per-token 1 / rms (consumer side)
   // [SQ_FLOATS] squared outputs (producer side): in the ring, which is idle by then (only this
   // CTA touches its ring)
-  float* sq = (float*)gen;
+  float* sq = (float*)(gen + (p.xstage_in_ring ? xbytes : 0u));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BM, split = blockIdx.z;
@@ -269,6 +275,12 @@ k_gemm_dec(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CU
   // (stable until this kernel's last CTA has seen every other CTA finish)
   uint32_t parity = 0;
   if (p.out_mode == 3 && warp >= 2) parity = peer_push_parity(p.push);
+  if (cluster && p.xstage_in_ring) {
+    // every thread of every CTA of the cluster is here only after its CTA's loads have landed
+    // and its MMAs have read them: from here on the rings may be written by the peers
+    __syncwarp();
+    cluster_sync_all();
+  }
   if (warp >= 2 && acc_ok) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -417,7 +429,10 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   const int splits = dec_splits(tiles, kb_total);
   const int kb_per = (kb_total + splits - 1) / splits;
   const size_t wbytes = g.dual ? 2 * A_BYTES : A_BYTES;
-  const size_t stage = wbytes + (size_t)tn * BK * 2;
+  // up to 8 tokens: an 8-row activation box (1 KB instead of 2 per k block), which is what lets a
+  // fourth ring stage fit beside the exchange area at three CTAs per SM
+  const int x_rows = g.M <= 8 ? 8 : tn;
+  const size_t stage = wbytes + (size_t)x_rows * BK * 2;
   // about a third of an SM's shared memory per CTA, so the next GEMM's CTAs can be resident
   // (and prefetching their weights) while this one computes
   // (the paired gate/up GEMM carries two weight tiles per stage, so the same budget would
@@ -425,26 +440,36 @@ int gemm_dec(cg_ctx* c, const DecGemm& g) {
   // The split-K exchange area (written by the other CTAs of the cluster, so outside the ring)
   // comes out of the same budget: three CTAs per SM may use 75 KB each, two 113 KB each.
   const int xstage_cols = splits > 1 ? (int)std::min<int64_t>(tn, g.M) : 0;
-  const size_t xbytes = (size_t)(g.dual ? 2 : 1) * xstage_cols * BM * 4;
-  const size_t fixed = 1024 + 16 * 8 + 64 + 128;
+  const bool x_in_ring = tn == 32;  // above 16 tokens a separate area would cost the ring a stage (measured: 3 % per step)
+  const size_t xarea = (size_t)(g.dual ? 2 : 1) * xstage_cols * BM * 4;
+  const size_t xbytes = x_in_ring ? 0 : xarea;
+  // (with the 8-row box the MMA of the last stage reads 1 KB past its activation slot: keep that inside the allocation)
+  const size_t fixed = 1024 + 16 * 8 + 64 + 128 + (x_rows < tn ? 1024 : 0);
   // (smaller budgets -- 57 or 43 KB, 78 KB for the pair -- were measured 2-5 % slower per step)
   const size_t budget = (g.dual ? 113 * 1024 : 75 * 1024) - fixed;
   int stages = (int)std::max<size_t>(2, (budget > xbytes ? budget - xbytes : 0) / stage);
+  // The paired kernel: three stages leave room for two CTAs per SM and nothing else, so when its
+  // CTAs fill nearly all of those slots it takes two stages, and the next kernel's CTAs fit beside it
+  // and fetch their weights early (Gemma-2-2B shape, 288 CTAs: 2.40 -> 2.25 ms per step; the
+  // Llama-3.2-1B shape, 256 CTAs, measured 1-2 % better with three).
+  if (g.dual && tiles * splits > 7 * 148 / 4) stages = std::min(stages, 2);
   stages = std::min(stages, std::max(kb_per, 2));
   stages = std::min(stages, 8);
   // the squared-output staging of the norm hand-over lives in the ring
-  while (g.ss_out && (size_t)SQ_FLOATS * 4 > (size_t)stages * stage) ++stages;
+  while ((g.ss_out || x_in_ring) && (x_in_ring ? xarea : 0) + (g.ss_out ? (size_t)SQ_FLOATS * 4 : 0) > (size_t)stages * stage) ++stages;
   const size_t smem = (size_t)stages * stage + xbytes + fixed;
 
   CUtensorMap mw, mx;
   CG_TRY(make_map(c, &mw, g.w, g.w_rows, g.K, g.ldw, BM));
-  CG_TRY(make_map(c, &mx, g.x, g.M, g.K, g.ldx, tn));
+  CG_TRY(make_map(c, &mx, g.x, g.M, g.K, g.ldx, x_rows));
   DecArgs a;
   a.out = g.out; a.ldo = g.ldo; a.residual = g.residual; a.out_mode = g.out_mode;
   a.dual = g.dual; a.act = g.act; a.up_off = (int)g.N;
   a.M = (int)g.M; a.N = (int)g.N; a.K = (int)g.K;
   a.kb_total = kb_total; a.kb_per_split = kb_per; a.splits = splits; a.stages = stages;
+  a.x_rows = x_rows;
   a.xstage_cols = xstage_cols;
+  a.xstage_in_ring = x_in_ring && splits > 1 ? 1 : 0;
   a.err = c->core->dev_err;
   a.trace = c->trace_on ? (int)(c->trace_next++ % TRACE_SLOTS) : -1;
   a.total_ctas = (int)(tiles * splits);
