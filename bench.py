@@ -368,7 +368,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp", "ep"],
                     help="with several GPUs: tp = the model is tensor-parallel over the ranks; dp = every rank holds the whole model and runs its share of the batch rows, no "
-                         "collective on the data path (what pays for a model this small: see DESIGN.md); ep (mixture-of-experts "
+                         "collective on the data path (what pays for a model this small: its decode step is bound by dependent latency, not bytes); ep (mixture-of-experts "
                          "workloads) = data-parallel attention with the experts split over the ranks, rows all-gathered and expert "
                          "sums reduce-scattered on every expert layer; auto (default) = the fastest of these for the model and batch by "
                          "the rule in choose_parallelism(): tp where the weight stream dominates a decode step, rows split otherwise")
