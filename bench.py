@@ -225,8 +225,8 @@ def choose_parallelism(asked: str, cfg, batch: int, world: int) -> str:
     split (tp).  Where it does not (the 1B shape: 2.5 GB, 0.38 ms of a 0.9 ms step) every GPU keeps
     the whole model and takes its share of the batch rows (dp): nothing crosses NVLink on the data
     path, prefill divides by the number of GPUs and decode steps run on fewer rows.  Mixture-of-
-    experts models split the experts and the rows (ep).  Measured on the 1B shape at 2 GPUs: dp
-    45.6 k tok/s, tp 31.2 k, one GPU 41.7 k."""
+    experts models split the experts and the rows (ep).  Measured on the 1B shape: one GPU 45.2 k
+    tok/s; two GPUs dp 47.9 k, tp 32.8 k; four GPUs dp 51.1 k, tp 30.6 k."""
     if world == 1 or asked != "auto":
         return asked if asked != "auto" else "tp"
     rows_split = batch % world == 0
