@@ -39,6 +39,10 @@ struct KernelEnv {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
   __device__ __forceinline__ uint32_t cluster_rank(int s) const { return (uint32_t)s; }
+  // one item per CTA: partials are pushed into the finishing CTA's landing area
+  static constexpr bool kPush = true;
+  float* land;
+  __device__ __forceinline__ float* landing() const { return land; }
   // the projected row, and the position when it lives on the device, belong to the stream order
   const AttnDecArgs* args;
   __device__ __forceinline__ int64_t settle(int64_t) const {
@@ -53,6 +57,7 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
   extern __shared__ __align__(16) uint8_t smem[];
   KernelEnv env;
   env.args = &a;
+  env.land = (float*)(smem + attn_dec_smem_bytes<D>());
   // Before the dependency wait: the first tiles of cached keys and values can be on the way
   // while the projection GEMM still runs.  What makes that sound: every writer of the device-side
   // position (the one-thread state kernel, in plain stream order; the arg-max kernel, after its
@@ -65,15 +70,26 @@ __global__ void __launch_bounds__(128) k_attn_dec(AttnDecArgs a, float scale) {
 }
 
 template <int D>
-int launch(cg_ctx* c, const AttnDecArgs& a) {
+int launch(cg_ctx* c, const AttnDecArgs& args) {
   constexpr int LD = D + 8;
   constexpr int KT = D > 128 ? 16 : 32;
-  const size_t smem = attn_dec_smem_bytes<D>();
+  AttnDecArgs a = args;
+  // The push form of the slice merge needs a landing area nothing else uses; it is taken only
+  // where that does not cost a resident CTA per SM (head size 128 would drop from three to two,
+  // which measured 1 % slower per step on the mixture-of-experts shape).
+  const int rep = a.nh / a.nkv;
+  const int blocks = a.splits * ((rep * D + 128 * a.splits - 1) / (128 * a.splits));
+  const size_t land = (size_t)(8 * MAX_REP * 2 + blocks * 128) * 4;
+  auto per_sm = [](size_t bytes) { return (227 * 1024) / (bytes + 1024); };
+  a.push_merge = a.splits > 1 && a.splits <= 8 && land <= attn_dec_landing_bytes() &&
+                 per_sm(attn_dec_smem_bytes<D>() + land) == per_sm(attn_dec_smem_bytes<D>());
+  const size_t smem = attn_dec_smem_bytes<D>() + (a.push_merge ? land : 0);
   static_assert(attn_dec_smem_bytes<D>() == (size_t)(16 * LD + 8 * KT * LD) * 2 + (size_t)(2 * D + 8 * MAX_REP + 16) * 4, "layout");
   static PerDeviceFlag configured_on;
   bool& configured = configured_on.at(c->core->device);
-  if (!configured && smem > 48 * 1024) {
-    CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (!configured && attn_dec_smem_bytes<D>() + attn_dec_landing_bytes() > 48 * 1024) {
+    CG_CUDA(c, cudaFuncSetAttribute(k_attn_dec<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)(attn_dec_smem_bytes<D>() + attn_dec_landing_bytes())));
     configured = true;
   }
   static PerDeviceFlag wide_on;

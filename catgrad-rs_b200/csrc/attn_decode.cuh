@@ -9,6 +9,10 @@
 //   sync_group()     barrier among the CTAs that hold the slices of one (row, kv head),
 //                    including a barrier among each CTA's own 128 threads
 //   cluster_rank(s)  cluster rank of the CTA that holds slice s
+//   kPush / landing()  kPush: the slices' partial results are PUSHED into a landing area (of
+//                    attn_dec_landing_bytes(), shared memory that nothing else uses) of the CTA that
+//                    finishes them, so one group barrier suffices and nobody waits before leaving;
+//                    otherwise the finishing CTA reads the partials where they lie (two barriers)
 //   settle(pos)      called once the first K/V tiles have been requested with a position that may
 //                    be one step old: waits for whatever the caller's inputs depend on and returns
 //                    the position to use (cached keys never change, so an early request is either
@@ -36,6 +40,10 @@ template <int D>
 __host__ __device__ constexpr size_t attn_dec_smem_bytes() {
   return (size_t)(16 * (D + 8) + 8 * (D > 128 ? 16 : 32) * (D + 8)) * 2 + (size_t)(2 * D + 8 * ATTN_MAX_REP + 16) * 4;
 }
+
+// landing area of the push form: {max, sum} per source slice and head, then per source slice the
+// output values the CTA finishes (at most 8 slices; up to rep * D / 128 + 8 blocks of 128 values)
+__host__ __device__ constexpr size_t attn_dec_landing_bytes() { return (size_t)(8 * ATTN_MAX_REP * 2 + (16 + 8) * 128) * 4; }
 
 // KT = keys per warp tile: 32, or 16 for head size 256 so that a CTA's tiles fit a third of an
 // SM's shared memory.
@@ -301,6 +309,23 @@ __device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale,
   // this slice's partial: part[r] = {max, sum}, part_o[r][e], left in shared memory for the cluster
   float* part_ml = (float*)vt;                 // [MAX_REP][2]
   float* part_o = part_ml + 2 * MAX_REP;       // [MAX_REP][D]
+  const int S = a.splits;
+  const bool push = Env::kPush && a.push_merge && S > 1;
+  // push form: output i is finished by slice (i / 128) % S, as its block number (i / 128) / S
+  const int kmax = (rep * D + 128 * S - 1) / (128 * S);
+  float* land_ml = nullptr;   // [8][MAX_REP][2]
+  float* land_o = nullptr;    // [S][kmax][128]
+  uint32_t land_u = 0;
+  if (push) {
+    land_ml = env.landing();
+    land_o = land_ml + 8 * MAX_REP * 2;
+    land_u = (uint32_t)__cvta_generic_to_shared(land_ml);
+  }
+  auto st_remote = [&](uint32_t local_addr, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  };
   for (int i = tid; i < rep * D; i += 128) {
     const int r = i / D, e = i - r * D;
     float mm = -INFINITY;
@@ -312,10 +337,48 @@ __device__ __forceinline__ void attn_dec_item(const AttnDecArgs& a, float scale,
       ll += red_l[w * MAX_REP + r] * f;
       oo += red_o[(w * MAX_REP + r) * D + e] * f;
     }
+    if (push) {
+      const int blk = i >> 7;
+      st_remote(land_u + (uint32_t)(8 * MAX_REP * 2 + ((split * kmax + blk / S) << 7) + (i & 127)) * 4u, env.cluster_rank(blk % S), oo);
+      if (e == 0)
+        for (int s = 0; s < S; ++s) {
+          st_remote(land_u + (uint32_t)((split * MAX_REP + r) * 2) * 4u, env.cluster_rank(s), mm);
+          st_remote(land_u + (uint32_t)((split * MAX_REP + r) * 2 + 1) * 4u, env.cluster_rank(s), ll);
+        }
+      continue;
+    }
     if (e == 0) { part_ml[2 * r] = mm; part_ml[2 * r + 1] = ll; }
     part_o[r * D + e] = oo;
   }
-  const int S = a.splits;
+  if (push) {
+    // one barrier: every slice's pushes are visible after it and nobody touches another CTA's
+    // shared memory again
+    env.sync_group();
+    int k = 0;
+    for (int i = tid + 128 * split; i < rep * D; i += 128 * S, ++k) {
+      const int r = i / D;
+      float ms[8], ls[8], os[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const bool in = s < S;
+        ms[s] = in ? land_ml[(s * MAX_REP + r) * 2] : -INFINITY;
+        ls[s] = in ? land_ml[(s * MAX_REP + r) * 2 + 1] : 0.f;
+        os[s] = in ? land_o[((s * kmax + k) << 7) + tid] : 0.f;
+      }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) mm = fmaxf(mm, ms[s]);
+      float ll = 0.f, oo = 0.f;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float f = ms[s] == -INFINITY ? 0.f : __expf(ms[s] - mm);
+        ll += ls[s] * f;
+        oo += os[s] * f;
+      }
+      a.out[(b * a.nh + kvh * rep + r) * (int64_t)D + (i - r * D)] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+    }
+    return;
+  }
   if (S == 1) {
     env.sync_cta();
     for (int i = tid; i < rep * D; i += 128) {

@@ -205,6 +205,9 @@ struct ResidentAttnEnv {
   }
   __device__ __forceinline__ uint32_t cluster_rank(int s) const { return (uint32_t)(base + s); }
   __device__ __forceinline__ int64_t settle(int64_t pos) const { return pos; }  // the phase barrier came first
+  // items follow one another in a CTA: partials are read where they lie, behind two barriers
+  static constexpr bool kPush = false;
+  __device__ __forceinline__ float* landing() const { return nullptr; }
 };
 
 template <int TN, int D>
@@ -508,7 +511,7 @@ __global__ void __launch_bounds__(R_THREADS, 1) k_decode_resident(const __grid_c
         a.qkv = p.qkv; a.cos_t = L.cos_t; a.sin_t = L.sin_t; a.q_gamma = L.q_gamma; a.k_gamma = L.k_gamma;
         a.norm_eps = p.eps; a.norm_plus_one = p.plus_one; a.k_cache = L.k_cache; a.v_cache = L.v_cache; a.out = p.att;
         a.pos_dev = nullptr; a.pos0 = pos0 + step; a.Tmax = p.Tmax; a.B = p.M; a.nh = p.nh; a.nkv = p.nkv; a.d = D;
-        a.window = L.window; a.softcap = p.attn_softcap; a.splits = p.attn_group;
+        a.window = L.window; a.softcap = p.attn_softcap; a.splits = p.attn_group; a.push_merge = 0;
         const int groups_per_cluster = R_CS / p.attn_group;
         const int n_groups = p.n_clusters * groups_per_cluster;
         const int pairs = p.M * p.nkv;

@@ -430,6 +430,7 @@ int run_layers(cg_decoder* D, int64_t B, int64_t S, int64_t pos0, bool from_dev_
     const bool windowed = cfg.sliding_window > 0 && (cfg.window_every <= 1 || (li % cfg.window_every) != cfg.window_every - 1);
     if (S == 1) {
       AttnDecArgs f;
+      f.push_merge = 0;  // (chosen by the launcher)
       f.qkv = (const float*)D->qkvb->data();
       f.cos_t = cos_t;
       f.sin_t = sin_t;

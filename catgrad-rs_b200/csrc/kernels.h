@@ -106,6 +106,7 @@ struct AttnDecArgs {
   int64_t window;                // 0 = none
   float softcap;                 // 0 = none
   int splits;                    // grid z = cluster size: context slices per (row, kv head)
+  int push_merge;                // set by the launcher: the slices' partials are pushed to the finishing CTA
 };
 // Rope + cache append + attention + merge of one new token per row, in one launch.
 int k_launch_attn_dec(cg_ctx* c, const AttnDecArgs& a);
