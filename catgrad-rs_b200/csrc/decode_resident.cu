@@ -107,7 +107,6 @@ struct RArgs {
   unsigned long long* trace;
   int trace_cap, trace_cta;
   int prefetch_ahead;  // stages the L2 prefetcher may run ahead of the weight producer (0 = no prefetch)
-  int dbg_kk;  // timing experiments only: MMAs issued per stage (4 = all; fewer gives wrong results)
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -368,7 +367,7 @@ __global__ void __launch_bounds__(R_THREADS, 1) k_decode_resident(const __grid_c
                 else umma_bf16_acc(d, da, db, idesc);
 #pragma unroll
                 for (int kk = 1; kk < BK / UMMA_K; ++kk)
-                  if (kk < p.dbg_kk) umma_bf16_acc(d, da + (uint64_t)(kk * (UMMA_K * 2 >> 4)), db + (uint64_t)(kk * (UMMA_K * 2 >> 4)), idesc);
+                  umma_bf16_acc(d, da + (uint64_t)(kk * (UMMA_K * 2 >> 4)), db + (uint64_t)(kk * (UMMA_K * 2 >> 4)), idesc);
                 umma_commit(b_empty + 8 * rp.s);
                 rp.advance((uint32_t)NST);
               }
@@ -863,7 +862,6 @@ int decode_resident_prepare(cg_ctx* c, const ResidentModel& m, int64_t M, Reside
   a.trace_cap = TRACE_CAP;
   a.trace_cta = 0;
   a.prefetch_ahead = getenv("CG_RES_PREFETCH") ? atoi(getenv("CG_RES_PREFETCH")) : 0;
-  a.dbg_kk = getenv("CG_DBG_KK") ? atoi(getenv("CG_DBG_KK")) : 4;
   pl->trace_area = (unsigned long long*)(basep + mp_bytes + ph_bytes + ly_bytes + 128);
   a.n_phases = (int)phases.size();
   a.n_steps = 0;

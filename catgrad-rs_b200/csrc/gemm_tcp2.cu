@@ -31,7 +31,6 @@
 // Every wait is bounded (tc_common.cuh); after an expiry all roles of both CTAs leave their
 // loops, meet at the closing cluster barrier, free TMEM and return.
 #include <algorithm>
-#include <cstdlib>
 
 #include "act.cuh"
 #include "tc_common.cuh"
@@ -421,12 +420,7 @@ int gemm_tcp2(cg_ctx* c, const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat1
   a.n_tiles = (int)((N + (glu ? 127 : 255)) / (glu ? 128 : 256));
   a.row2_off = (int)N;
   a.act = act;
-  static const int stages_env = [] {
-    const char* e = getenv("CG_PAIR_STAGES");
-    const int v = e ? atoi(e) : P2_MAX_STAGES;
-    return v >= 2 && v <= P2_MAX_STAGES ? v : P2_MAX_STAGES;
-  }();
-  a.stages = stages_env;
+  a.stages = P2_MAX_STAGES;  // (six stages measured the same as seven)
   a.err = c->core->dev_err;
   const int64_t tiles = (int64_t)a.m_tiles * a.n_tiles;
   if (tiles > 2147483647ll) return fail(c, CG_ERR_UNSUPPORTED, "gemm_tcp2: too many tiles");
