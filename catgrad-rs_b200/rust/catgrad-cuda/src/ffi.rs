@@ -54,4 +54,6 @@ extern "C" {
     pub fn cg_sync(ctx: C) -> i32;
     pub fn cg_set_option(ctx: C, name: *const c_char, value: i64) -> i32;
     pub fn cg_lazy_stats(ctx: C, recorded: *mut i64, fused: *mut i64, pending: *mut i64) -> i32;
+    pub fn cg_linear(ctx: C, x: *const cg_tensor, w: *const cg_tensor, out: *mut T) -> i32;
+    pub fn cg_linear_glu(ctx: C, x: *const cg_tensor, w: *const cg_tensor, act: i32, out: *mut T) -> i32;
 }

@@ -82,6 +82,19 @@ impl CudaBackend {
         self.check(unsafe { ffi::cg_lazy_stats(self.ctx.0, &mut a, &mut b, &mut c) });
         (a, b, c)
     }
+    /// y = x W^T for a weight stored [out, in] (tensor cores when W is stored bf16): what
+    /// `linear_no_bias` lowers to, without the transposed view.
+    pub fn linear(&self, x: &CudaTensor, w: &CudaTensor) -> CudaTensor {
+        let mut out = std::ptr::null_mut();
+        self.check(unsafe { ffi::cg_linear(self.ctx.0, x.raw(), w.raw(), &mut out) });
+        CudaTensor::from_raw(out)
+    }
+    /// act(x Wg^T) * (x Wu^T) for the stacked weight [2F, in] (gate rows first); act 0 = silu, 1 = tanh gelu.
+    pub fn linear_glu(&self, x: &CudaTensor, w_gate_up: &CudaTensor, act: i32) -> CudaTensor {
+        let mut out = std::ptr::null_mut();
+        self.check(unsafe { ffi::cg_linear_glu(self.ctx.0, x.raw(), w_gate_up.raw(), act, &mut out) });
+        CudaTensor::from_raw(out)
+    }
     /// Run everything pending and surface device-side errors.
     pub fn sync(&self) { self.check(unsafe { ffi::cg_sync(self.ctx.0) }); }
     pub(crate) fn raw_ctx(&self) -> *mut ffi::cg_ctx { self.ctx.0 }
